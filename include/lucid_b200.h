@@ -1,0 +1,94 @@
+/* C ABI of the B200 (sm_100a) LUCID forward-substitution library.
+ *
+ * These entry points are what a binding of the reference's operator layer
+ * (lucid_kernels/cute/forward_sub_interface.py) calls instead of JIT-compiling and launching its
+ * CuTe-DSL kernels.  Plain pointers and sizes only; every device pointer must belong to the current
+ * CUDA device; all work is enqueued on `cuda_stream` (a cudaStream_t) and nothing synchronises
+ * unless stated.
+ *
+ * Tensors are (B, N, H, 128) fp16 or bf16 with a contiguous last dimension ("BSHD"); `*_strides`
+ * give the element strides of the first three dimensions {batch, sequence, head}.  Base addresses
+ * must be 16-byte aligned and the strides multiples of 8 elements.  N must be a multiple of 128.
+ *
+ * Return value: 0 on success, a negative LUCID_E_* code for a rejected argument, or a positive
+ * cudaError_t from the runtime.  Device-side waits are bounded; a wait that runs out does not hang
+ * the GPU but is recorded in the workspace and reported by lucid_read_status().
+ */
+#ifndef LUCID_B200_H_
+#define LUCID_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LUCID_DTYPE_FP16 0
+#define LUCID_DTYPE_BF16 1
+
+/* flags */
+#define LUCID_FLAG_DIAG_SOLVE 1   /* apply inv(tril(exp(K_i K_i^T))) on the diagonal blocks           */
+#define LUCID_FLAG_NO_SYNC 2      /* skip inter-block flag waits (profiling only, results undefined)  */
+#define LUCID_FLAG_INSTRUMENT 4   /* record per-row-block timestamps in the workspace                  */
+
+/* backward modes */
+#define LUCID_BWD_DV_ONLY 0       /* dV only                                                          */
+#define LUCID_BWD_COMBINED 1      /* dV and the full dK (off-diagonal and diagonal terms)             */
+
+#define LUCID_E_BAD_SHAPE (-1)
+#define LUCID_E_BAD_DTYPE (-2)
+#define LUCID_E_BAD_ALIGNMENT (-3)
+#define LUCID_E_WORKSPACE_TOO_SMALL (-4)
+#define LUCID_E_NULL_POINTER (-5)
+#define LUCID_E_TENSOR_MAP (-6)
+#define LUCID_E_NO_DEVICE (-7)
+
+/* Bytes of scratch the calls below need for a (B, N, H, 128) problem.  The workspace holds the
+ * inter-block flags, the scheduler's control words, the per-block unit-triangular inverses
+ * (B*H*N*128 16-bit values) and their row scales.  Replaces the per-call torch.zeros / torch.empty
+ * allocations of forward_sub_interface.py:97-103,217-219,297-300 and the diag_inv tensor of :109-117. */
+size_t lucid_workspace_bytes(int B, int N, int H);
+
+/* V' = L^-1 V.  Replaces _forward_sub_fwd (forward_sub_interface.py:56-165): _compute_diag_inv (:30-53)
+ * and the ForwardSubSm90 launch (:153-158).  `window_blocks` <= 0 means full causality, otherwise
+ * only the last `window_blocks` blocks are subtracted (forward_sub_interface.py:69-70).
+ * `chain_group` = how many (batch, head) systems the scheduler advances together (0 = choose from the
+ * problem size so that their K and V' fit the L2 cache). */
+int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
+                  const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D, int dtype,
+                  int flags, int window_blocks, int chain_group, void* workspace, size_t workspace_bytes,
+                  void* cuda_stream);
+
+/* dV = L^-T dV' and, in LUCID_BWD_COMBINED mode, dK.  Replaces _forward_sub_bwd
+ * (forward_sub_interface.py:357-378): _compute_diag_inv_transpose (:177-193), the BackwardSubSm90
+ * launches of _forward_sub_bwd_dv (:196-268) / _forward_sub_bwd_combined (:271-354) and the host-side
+ * _add_diagonal_dk_correction (:381-405).  `dk` may be NULL in LUCID_BWD_DV_ONLY mode. */
+int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void* dv, void* dk,
+                  const int64_t k_strides[3], const int64_t vp_strides[3], const int64_t dvp_strides[3],
+                  const int64_t dv_strides[3], const int64_t dk_strides[3], int B, int N, int H, int D, int dtype,
+                  int flags, int mode, int chain_group, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Synchronises `cuda_stream` and copies the eight status words of the last call that used
+ * `workspace`: out[0] = 0 ok / 1 in-CTA barrier wait timed out / 2 a predecessor row-block was never
+ * published / 3 left early after another CTA's error; out[1] = kernel (0 prep, 1 solve, 2 dK);
+ * out[2] = (batch*H + head); out[3] = row-block; out[4] = detail (awaited row-block); out[5] = barrier
+ * id.  Returns 0 or a cudaError_t.  The reference has no counterpart: its waits spin forever
+ * (forward_sub_fwd.py:536-544). */
+int lucid_read_status(const void* workspace, void* cuda_stream, int32_t out[8]);
+
+/* Human-readable name of a status word out[0] or of a negative return code. */
+const char* lucid_status_string(int code);
+
+/* Sets the time limit (nanoseconds) of every device-side wait; default 2e9. */
+void lucid_set_wait_limit_ns(uint64_t ns);
+
+/* Offsets inside the workspace, for tools that read the instrumentation:
+ * timestamps are int64[(B*H)][T][8] = {start, loop end, published, ns spent in flag waits, CTA, tiles}
+ * (cf. the (T, 8) buffer of forward_sub_interface.py:103). */
+size_t lucid_workspace_timestamps_offset(int B, int N, int H);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUCID_B200_H_ */

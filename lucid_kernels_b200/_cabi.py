@@ -1,0 +1,132 @@
+"""ctypes binding of the C ABI declared in include/lucid_b200.h.
+
+The library is the only implementation: if it is missing, or no CUDA device is usable, calls raise.
+There is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Dict, Tuple
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lucid_b200.so")
+_lib = None
+_lock = threading.Lock()
+
+FLAG_DIAG_SOLVE = 1
+FLAG_NO_SYNC = 2
+FLAG_INSTRUMENT = 4
+BWD_DV_ONLY = 0
+BWD_COMBINED = 1
+
+_I64x3 = ctypes.c_int64 * 3
+
+EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_read_status",
+           "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset")
+
+
+class LucidKernelError(RuntimeError):
+    pass
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Load (once) and type the shared library.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(_LIB_PATH):
+            raise LucidKernelError(
+                f"{_LIB_PATH} not found: build it with `python -m lucid_kernels_b200.build` "
+                "(there is no fallback implementation)")
+        lib = ctypes.CDLL(_LIB_PATH)
+        c = ctypes
+        lib.lucid_workspace_bytes.restype = c.c_size_t
+        lib.lucid_workspace_bytes.argtypes = [c.c_int, c.c_int, c.c_int]
+        lib.lucid_workspace_timestamps_offset.restype = c.c_size_t
+        lib.lucid_workspace_timestamps_offset.argtypes = [c.c_int, c.c_int, c.c_int]
+        lib.lucid_fwd_sub.restype = c.c_int
+        lib.lucid_fwd_sub.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, _I64x3, _I64x3, _I64x3,
+                                      c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                                      c.c_void_p, c.c_size_t, c.c_void_p]
+        lib.lucid_bwd_sub.restype = c.c_int
+        lib.lucid_bwd_sub.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
+                                      _I64x3, _I64x3, _I64x3, _I64x3, _I64x3,
+                                      c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                                      c.c_void_p, c.c_size_t, c.c_void_p]
+        lib.lucid_read_status.restype = c.c_int
+        lib.lucid_read_status.argtypes = [c.c_void_p, c.c_void_p, c.POINTER(c.c_int32)]
+        lib.lucid_status_string.restype = c.c_char_p
+        lib.lucid_status_string.argtypes = [c.c_int]
+        lib.lucid_set_wait_limit_ns.restype = None
+        lib.lucid_set_wait_limit_ns.argtypes = [c.c_uint64]
+        _lib = lib
+    return _lib
+
+
+def strides3(t: torch.Tensor):
+    """Element strides {batch, sequence, head} of a (B, N, H, D) tensor."""
+    return _I64x3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float16:
+        return 0
+    if dt == torch.bfloat16:
+        return 1
+    raise AssertionError("inputs must be float16 or bfloat16")
+
+
+# One workspace per (device, stream, problem size): the kernels of one call communicate through it, so
+# two calls that may overlap on the GPU must not share one.
+_workspaces: Dict[Tuple[int, int, int, int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, stream_ptr: int, B: int, N: int, H: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr, B, N, H)
+    ws = _workspaces.get(key)
+    if ws is None:
+        nbytes = load().lucid_workspace_bytes(B, N, H)
+        # torch's caching allocator hands out 512-byte aligned blocks; over-allocate to reach 1 KiB
+        raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        off = (-raw.data_ptr()) % 1024
+        ws = raw[off:off + nbytes]
+        if len(_workspaces) > 64:
+            _workspaces.clear()
+        _workspaces[key] = ws
+    return ws
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    msg = load().lucid_status_string(rc).decode()
+    if rc > 0:
+        msg += f" (cudaError_t {rc})"
+    raise LucidKernelError(f"{what} failed: {msg}")
+
+
+def read_status(ws: torch.Tensor, stream_ptr: int):
+    """Synchronise the stream and return the eight status words of the last call on this workspace."""
+    out = (ctypes.c_int32 * 8)()
+    rc = load().lucid_read_status(ws.data_ptr(), stream_ptr, out)
+    check_rc(rc, "lucid_read_status")
+    return list(out)
+
+
+def raise_on_device_error(ws: torch.Tensor, stream_ptr: int, what: str) -> None:
+    st = read_status(ws, stream_ptr)
+    if st[0] != 0:
+        msg = load().lucid_status_string(st[0]).decode()
+        kern = {0: "diag-prep", 1: "solve", 2: "dK"}.get(st[1], "?")
+        raise LucidKernelError(
+            f"{what}: {msg} [kernel={kern} chain={st[2]} row_block={st[3]} detail={st[4]} barrier={st[5]}]")

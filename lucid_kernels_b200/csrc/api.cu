@@ -1,0 +1,269 @@
+// C ABI: argument checking, workspace carving, tensor maps and kernel launches.
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/lucid_b200.h"
+#include "kernels.h"
+#include "tmap.h"
+
+namespace lucid {
+
+static unsigned long long g_wait_ns = 2000000000ull;
+
+// ---- workspace layout ----------------------------------------------------------------------
+//   [0, 256)            three Control blocks: 0 = diag prep, 1 = solve, 2 = dK
+//   [256, 256 + 4*C*T)  flags
+//   X                   C*T tiles of 32 KiB (1 KiB aligned)
+//   lam_inv             C*T*128 fp32
+//   timestamps          C*T*8 int64
+struct Layout {
+  size_t flags, x, lam, ts, total;
+};
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static Layout make_layout(int B, int N, int H) {
+  const size_t CT = (size_t)B * H * (N / kBlock);
+  Layout l;
+  l.flags = 256;
+  l.x = align_up(l.flags + CT * 4, 1024);
+  l.lam = l.x + CT * kTileBytes;
+  l.ts = align_up(l.lam + CT * kBlock * 4, 256);
+  l.total = l.ts + CT * 8 * 8;
+  return l;
+}
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static int check_tensor(const void* p, const int64_t st[3]) {
+  if (!p || !st) return LUCID_E_NULL_POINTER;
+  if (reinterpret_cast<uintptr_t>(p) % 16) return LUCID_E_BAD_ALIGNMENT;
+  for (int i = 0; i < 3; ++i)
+    if (st[i] % 8 || st[i] < 0) return LUCID_E_BAD_ALIGNMENT;
+  return 0;
+}
+
+static int check_shape(int B, int N, int H, int D, int dtype) {
+  if (B <= 0 || N <= 0 || H <= 0 || D != kBlock || N % kBlock) return LUCID_E_BAD_SHAPE;
+  if ((long long)B * H * (N / kBlock) > (1ll << 30) / kBlock) return LUCID_E_BAD_SHAPE;
+  if (dtype != LUCID_DTYPE_FP16 && dtype != LUCID_DTYPE_BF16) return LUCID_E_BAD_DTYPE;
+  return 0;
+}
+
+// (B, N, H, 128) tensor -> 4-D map {d, n, h, b}
+static int bshd_map(CUtensorMap* m, bool bf16, const void* p, const int64_t st[3], int B, int N, int H,
+                    uint32_t box_rows) {
+  uint64_t dims[4] = {(uint64_t)kBlock, (uint64_t)N, (uint64_t)H, (uint64_t)B};
+  // size-1 dimensions may carry any stride; give them a harmless valid one
+  uint64_t sn = (uint64_t)st[1] * 2, sh = (uint64_t)st[2] * 2, sb = (uint64_t)st[0] * 2;
+  if (H == 1 || sh == 0) sh = 256;
+  if (B == 1 || sb == 0) sb = 256;
+  if (sn == 0) sn = 256;
+  uint64_t strides[3] = {sn, sh, sb};
+  return make_tmap_16bit(m, bf16, p, 4, dims, strides, box_rows) ? LUCID_E_TENSOR_MAP : 0;
+}
+
+static int auto_group(int C, int N, int requested) {
+  if (requested > 0) return requested < C ? requested : C;
+  // K and Y of one chain take N * 512 bytes; keep the group's working set near half of a 126 MB L2
+  const long long per_chain = (long long)N * 512;
+  long long g = (64ll << 20) / per_chain;
+  if (g < 1) g = 1;
+  if (g > C) g = C;
+  return (int)g;
+}
+
+static Problem make_problem(int B, int N, int H, int flags, int window, int group) {
+  Problem p;
+  p.B = B;
+  p.N = N;
+  p.H = H;
+  p.T = N / kBlock;
+  p.C = B * H;
+  p.group = auto_group(p.C, N, group);
+  p.use_diag = (flags & LUCID_FLAG_DIAG_SOLVE) ? 1 : 0;
+  p.window = window;
+  p.no_sync = (flags & LUCID_FLAG_NO_SYNC) ? 1 : 0;
+  p.instrument = (flags & LUCID_FLAG_INSTRUMENT) ? 1 : 0;
+  p.wait_ns = g_wait_ns;
+  return p;
+}
+
+// shared by forward and backward: prep (if diag) + one solve
+static int run_solve(bool reverse, const void* k, const void* in, void* out, const int64_t ks[3],
+                     const int64_t ins[3], const int64_t outs[3], const Problem& p, bool bf16, uint8_t* ws,
+                     const Layout& lay, cudaStream_t stream) {
+  const int CT = p.C * p.T;
+  Control* ctl = reinterpret_cast<Control*>(ws);
+  CUtensorMap tm_k, tm_in, tm_out, tm_x;
+  int rc;
+  if ((rc = bshd_map(&tm_k, bf16, k, ks, p.B, p.N, p.H, 128))) return rc;
+  if ((rc = bshd_map(&tm_in, bf16, in, ins, p.B, p.N, p.H, 128))) return rc;
+  if ((rc = bshd_map(&tm_out, bf16, out, outs, p.B, p.N, p.H, 64))) return rc;
+  {
+    uint64_t dims[2] = {(uint64_t)kBlock, (uint64_t)CT * kBlock};
+    uint64_t str[1] = {256};
+    if (make_tmap_16bit(&tm_x, bf16, ws + lay.x, 2, dims, str, 128)) return LUCID_E_TENSOR_MAP;
+  }
+  cudaError_t e;
+  if (p.use_diag) {
+    PrepArgs pa;
+    pa.x = ws + lay.x;
+    pa.lam_inv = reinterpret_cast<float*>(ws + lay.lam);
+    pa.ctl = ctl + 0;
+    pa.T = p.T;
+    pa.H = p.H;
+    pa.wait_ns = p.wait_ns;
+    if ((e = launch_diag_prep(bf16, tm_k, pa, CT, stream)) != cudaSuccess) return (int)e;
+  }
+  SolveArgs sa;
+  sa.out = out;
+  sa.out_strides = Strides{outs[0], outs[1], outs[2]};
+  sa.lam_inv = reinterpret_cast<const float*>(ws + lay.lam);
+  sa.flags = reinterpret_cast<int*>(ws + lay.flags);
+  sa.ctl = ctl + 1;
+  sa.timestamps = p.instrument ? reinterpret_cast<long long*>(ws + lay.ts) : nullptr;
+  sa.p = p;
+  const int sms = sm_count();
+  if (sms <= 0) return LUCID_E_NO_DEVICE;
+  const int grid = CT < sms ? CT : sms;
+  if ((e = launch_solve(bf16, reverse, tm_k, tm_in, tm_out, tm_x, sa, grid, stream)) != cudaSuccess) return (int)e;
+  return 0;
+}
+
+}  // namespace lucid
+
+using namespace lucid;
+
+extern "C" {
+
+size_t lucid_workspace_bytes(int B, int N, int H) {
+  if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
+  return make_layout(B, N, H).total;
+}
+
+size_t lucid_workspace_timestamps_offset(int B, int N, int H) {
+  if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
+  return make_layout(B, N, H).ts;
+}
+
+void lucid_set_wait_limit_ns(uint64_t ns) { g_wait_ns = ns; }
+
+int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
+                  const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D, int dtype,
+                  int flags, int window_blocks, int chain_group, void* workspace, size_t workspace_bytes,
+                  void* cuda_stream) {
+  int rc;
+  if ((rc = check_shape(B, N, H, D, dtype))) return rc;
+  if ((rc = check_tensor(k, k_strides)) || (rc = check_tensor(v, v_strides)) ||
+      (rc = check_tensor(v_prime, vp_strides)))
+    return rc;
+  if (!workspace) return LUCID_E_NULL_POINTER;
+  if (reinterpret_cast<uintptr_t>(workspace) % 1024) return LUCID_E_BAD_ALIGNMENT;
+  const Layout lay = make_layout(B, N, H);
+  if (workspace_bytes < lay.total) return LUCID_E_WORKSPACE_TOO_SMALL;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);   // control words + flags
+  if (e != cudaSuccess) return (int)e;
+  const Problem p = make_problem(B, N, H, flags, window_blocks, chain_group);
+  return run_solve(false, k, v, v_prime, k_strides, v_strides, vp_strides, p, dtype == LUCID_DTYPE_BF16, ws, lay,
+                   stream);
+}
+
+int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void* dv, void* dk,
+                  const int64_t k_strides[3], const int64_t vp_strides[3], const int64_t dvp_strides[3],
+                  const int64_t dv_strides[3], const int64_t dk_strides[3], int B, int N, int H, int D, int dtype,
+                  int flags, int mode, int chain_group, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  int rc;
+  if ((rc = check_shape(B, N, H, D, dtype))) return rc;
+  if (mode != LUCID_BWD_DV_ONLY && mode != LUCID_BWD_COMBINED) return LUCID_E_BAD_SHAPE;
+  if ((rc = check_tensor(k, k_strides)) || (rc = check_tensor(dv_prime, dvp_strides)) ||
+      (rc = check_tensor(dv, dv_strides)))
+    return rc;
+  if (mode == LUCID_BWD_COMBINED) {
+    if ((rc = check_tensor(v_prime, vp_strides)) || (rc = check_tensor(dk, dk_strides))) return rc;
+  }
+  if (!workspace) return LUCID_E_NULL_POINTER;
+  if (reinterpret_cast<uintptr_t>(workspace) % 1024) return LUCID_E_BAD_ALIGNMENT;
+  const Layout lay = make_layout(B, N, H);
+  if (workspace_bytes < lay.total) return LUCID_E_WORKSPACE_TOO_SMALL;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);
+  if (e != cudaSuccess) return (int)e;
+  const bool bf16 = dtype == LUCID_DTYPE_BF16;
+  const Problem p = make_problem(B, N, H, flags, 0, chain_group);
+  if ((rc = run_solve(true, k, dv_prime, dv, k_strides, dvp_strides, dv_strides, p, bf16, ws, lay, stream)))
+    return rc;
+  if (mode == LUCID_BWD_COMBINED) {
+    CUtensorMap tm_k, tm_vp, tm_dv;
+    if ((rc = bshd_map(&tm_k, bf16, k, k_strides, B, N, H, 128))) return rc;
+    if ((rc = bshd_map(&tm_vp, bf16, v_prime, vp_strides, B, N, H, 128))) return rc;
+    if ((rc = bshd_map(&tm_dv, bf16, dv, dv_strides, B, N, H, 128))) return rc;
+    DkArgs da;
+    da.dk = dk;
+    da.dk_strides = Strides{dk_strides[0], dk_strides[1], dk_strides[2]};
+    da.ctl = reinterpret_cast<Control*>(ws) + 2;
+    da.p = p;
+    const int sms = sm_count();
+    if (sms <= 0) return LUCID_E_NO_DEVICE;
+    const int CT = p.C * p.T;
+    const int grid = CT < sms ? CT : sms;
+    if ((e = launch_dk(bf16, tm_k, tm_vp, tm_dv, da, grid, stream)) != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+int lucid_read_status(const void* workspace, void* cuda_stream, int32_t out[8]) {
+  if (!workspace || !out) return LUCID_E_NULL_POINTER;
+  int32_t host[24];
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return (int)e;
+  memset(out, 0, 8 * sizeof(int32_t));
+  for (int kern = 0; kern < 3; ++kern) {
+    const int32_t* c = host + kern * 8;   // {ticket, status[7]}
+    if (c[1] != 0) {
+      out[0] = c[1];
+      out[1] = kern;
+      out[2] = c[2];
+      out[3] = c[3];
+      out[4] = c[4];
+      out[5] = c[5];
+      out[6] = c[0];
+      return 0;
+    }
+  }
+  return 0;
+}
+
+const char* lucid_status_string(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case 1: return "device-side barrier wait timed out";
+    case 2: return "a predecessor row-block was never published (flag wait timed out)";
+    case 3: return "kernel left early after another CTA reported an error";
+    case LUCID_E_BAD_SHAPE: return "bad shape: need B,N,H > 0, head_dim == 128, N % 128 == 0";
+    case LUCID_E_BAD_DTYPE: return "bad dtype: need fp16 (0) or bf16 (1)";
+    case LUCID_E_BAD_ALIGNMENT: return "bad alignment: 16-byte aligned bases, strides multiples of 8 elements";
+    case LUCID_E_WORKSPACE_TOO_SMALL: return "workspace too small (see lucid_workspace_bytes)";
+    case LUCID_E_NULL_POINTER: return "null pointer";
+    case LUCID_E_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected a tensor";
+    case LUCID_E_NO_DEVICE: return "no CUDA device";
+    default: return code > 0 ? "CUDA runtime error" : "unknown";
+  }
+}
+
+}  // extern "C"

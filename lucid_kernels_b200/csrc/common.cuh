@@ -1,0 +1,128 @@
+// Shared definitions for the LUCID kernels: problem description, workspace layout, status reporting
+// and bounded waits.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "ptx.cuh"
+
+namespace lucid {
+
+constexpr int kBlock = 128;          // rows per block == head_dim
+constexpr int kTileBytes = 32768;    // one 128 x 128 16-bit tile
+constexpr int kHalfBytes = 16384;    // one 64-column panel (or 64-row half) of a tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+// status codes written to the status buffer (word 0 = code, words 1.. = location)
+enum : int {
+  kOk = 0,
+  kErrBarrierTimeout = 1,   // an in-CTA mbarrier wait ran out of time
+  kErrFlagTimeout = 2,      // a row-block's predecessor was never published
+  kErrAborted = 3,          // left early because another CTA reported an error
+};
+
+// Control words at the start of the workspace (int32 each).
+struct Control {
+  int ticket;        // next work item
+  int status[7];     // [0] code, [1] chain, [2] row-block, [3] detail, [4] barrier id, [5..6] spare
+};
+
+// Element strides (in elements, not bytes) of a (B, N, H, 128) tensor whose last dim is contiguous.
+struct Strides {
+  long long b, n, h;
+};
+
+struct Problem {
+  int B, N, H, T;    // T = N / 128
+  int C;             // chains = B * H
+  int group;         // chains advanced together by the scheduler
+  int use_diag;      // apply the diagonal-block solve
+  int window;        // forward only: number of previous blocks used (<= 0: all)
+  int no_sync;       // skip flag waits (profiling only; results are then meaningless)
+  int instrument;    // write per-row-block timestamps
+  unsigned long long wait_ns;  // time limit of every device-side wait
+};
+
+// ---------------------------------------------------------------------------------------------
+// error reporting and bounded waits
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void report_error(Control* ctl, int code, int chain, int row, int detail, int bar_id) {
+  if (atomicCAS(&ctl->status[0], 0, code) == 0) {
+    ctl->status[1] = chain;
+    ctl->status[2] = row;
+    ctl->status[3] = detail;
+    ctl->status[4] = bar_id;
+    __threadfence();
+  }
+}
+
+// Wait for an mbarrier phase with a time limit.  Returns false (after flagging the CTA-wide abort
+// word) when the limit runs out or another role of this CTA has already given up.
+__device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, volatile int* cta_abort, Control* ctl,
+                                             unsigned long long limit_ns, int chain, int row, int bar_id) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0) {
+      if (*cta_abort) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        *cta_abort = 1;
+        report_error(ctl, kErrBarrierTimeout, chain, row, 0, bar_id);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Wait until flag != 0 (acquire).  Polls the global status word so that one CTA's failure releases
+// every waiter.  Returns the nanoseconds spent waiting through *waited when it is non-null.
+__device__ __forceinline__ bool wait_flag(const int* flag, volatile int* cta_abort, Control* ctl,
+                                          unsigned long long limit_ns, int chain, int row, int dep_row,
+                                          unsigned long long* waited) {
+  if (ld_acquire_gpu(flag) != 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  bool ok = true;
+  while (ld_acquire_gpu(flag) == 0) {
+    if ((++spins & 63u) == 0) {
+      if (*cta_abort) { ok = false; break; }
+      if (ld_relaxed_gpu(&ctl->status[0]) != 0) {
+        *cta_abort = 1;
+        ok = false;
+        break;
+      }
+      if (globaltimer_ns() - t0 > limit_ns) {
+        *cta_abort = 1;
+        report_error(ctl, kErrFlagTimeout, chain, row, dep_row, -1);
+        ok = false;
+        break;
+      }
+    }
+    __nanosleep(20);
+  }
+  if (waited) *waited += globaltimer_ns() - t0;
+  return ok;
+}
+
+// Work item t -> (chain, step).  Chains are advanced in groups of `group`; inside a group the order
+// is step-major, so an item's predecessors (same chain, smaller step) always have smaller tickets.
+__device__ __forceinline__ bool decode_ticket(int t, int C, int T, int group, int& chain, int& step) {
+  if (t >= C * T) return false;
+  const int per = group * T;
+  const int g = t / per;
+  const int base = g * group;
+  const int gsz = min(group, C - base);
+  const int tl = t - g * per;
+  step = tl / gsz;
+  chain = base + tl % gsz;
+  return true;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
+}  // namespace lucid

@@ -1,0 +1,377 @@
+// dK of the LUCID block-triangular solve on sm_100a.  Replaces the dK half of the reference's
+// BackwardSubSm90 (lucid_kernels/cute/forward_sub_bwd.py:1113-1269, Phase 1 upper-triangle and Phase 2
+// lower-triangle accumulation) and the host-side diagonal term _add_diagonal_dk_correction
+// (lucid_kernels/cute/forward_sub_interface.py:381-405), which here runs on the device in the same loop.
+//
+// With E_ij = exp(K_i K_j^T) and dV already solved,
+//     dK_i = sum_{j<i} W_ij K_j + sum_{j>i} W_ij K_j + (D1 + D2) K_i
+//     W_ij = -(dV_i V'_j^T) o E_ij   (j < i)          W_ij = -(V'_i dV_j^T) o E_ij   (j > i)
+//     D1   = tril(-(dV_i V'_i^T) o E_ii)               D2   = triu(-(V'_i dV_i^T) o E_ii) = D1^T
+// so every term is "S = K_i K_j^T, G = A_i Z_j^T, W = -exp(S) o G (masked on the diagonal), ACC += W K_j"
+// with (A, Z) = (dV, V') for the lower part and (V', dV) for the upper part.  Row-blocks are independent:
+// no flags, no ordering; a CTA owns row-block i and streams all T blocks j past it (T + 1 tiles).
+//
+// Warp roles (384 threads): warp 0 producer (tickets, K_i, A_i, K_j ring of 3, Z_j ring of 2), warp 1
+// MMA issuer and TMEM owner, warps 4-11 form W: both groups work on the same tile, 64 columns each.
+#include <type_traits>
+#include "kernels.h"
+
+namespace lucid {
+
+struct DkSmem {
+  alignas(1024) uint8_t ki[kTileBytes];        // K_i
+  alignas(1024) uint8_t ai[kTileBytes];        // dV_i for the lower part, then V'_i for the upper part
+  alignas(1024) uint8_t kring[3][kTileBytes];  // K_j
+  alignas(1024) uint8_t zring[2][kTileBytes];  // V'_j (lower) or dV_j (upper)
+  alignas(8) uint64_t k_full[3];
+  uint64_t k_empty[3], z_full[2], z_empty[2];
+  uint64_t ki_full, ki_free, ai_full, ai_free;
+  uint64_t s_full[2], g_full, w_full;
+  uint64_t acc_full, acc_free;
+  uint64_t tk_full[2], tk_empty[2];
+  int tk_slot[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+enum DkBar : int {
+  DK_K_FULL = 201, DK_K_EMPTY, DK_Z_FULL, DK_Z_EMPTY, DK_KI_FULL, DK_KI_FREE, DK_AI_FULL, DK_AI_FREE, DK_S_FULL,
+  DK_G_FULL, DK_W_FULL, DK_ACC_FULL, DK_ACC_FREE, DK_TK_FULL, DK_TK_EMPTY
+};
+
+constexpr int kDkThreads = 384;
+constexpr int kDkS0 = 0, kDkS1 = 128, kDkG = 256, kDkAcc = 384;
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kDkThreads, 1)
+dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
+          const __grid_constant__ CUtensorMap tm_vp,   // V',  box 64 x 128
+          const __grid_constant__ CUtensorMap tm_dv,   // dV,  box 64 x 128
+          const DkArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  DkSmem& s = *reinterpret_cast<DkSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const Problem& P = args.p;
+  Control* ctl = args.ctl;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int T = P.T, H = P.H;
+  const unsigned long long limit = P.wait_ns;
+  volatile int* cta_abort = &s.abort_flag;
+  // With identity diagonal blocks (use_diag == 0) the operator has no diagonal-block dependence on K.
+  const bool diag_tiles = P.use_diag != 0;
+
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&s.k_full[i], 1);
+      mbar_init(&s.k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.z_full[i], 1);
+      mbar_init(&s.z_empty[i], 1);
+      mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.tk_full[i], 1);
+      mbar_init(&s.tk_empty[i], 9);
+    }
+    mbar_init(&s.ki_full, 1);
+    mbar_init(&s.ki_free, 1);
+    mbar_init(&s.ai_full, 1);
+    mbar_init(&s.ai_free, 1);
+    mbar_init(&s.g_full, 1);
+    mbar_init(&s.w_full, 256);
+    mbar_init(&s.acc_full, 1);
+    mbar_init(&s.acc_free, 256);
+    s.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+
+  // Tile q of row-block i (n tiles): the lower part j = 0..i-1, [D1, D2 at j = i], the upper part.
+  //   n_low = i (+1 with D1); tiles q < n_low are "lower" (A = dV_i, Z = V'_j).
+  auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& n_low) -> bool {
+    if (ticket >= P.C * T) return false;
+    chain = ticket / T;
+    i = ticket % T;
+    n_low = i + (diag_tiles ? 1 : 0);
+    n = T - 1 + (diag_tiles ? 2 : 0);
+    return true;
+  };
+  auto tile_j = [&](int i, int n_low, int q) -> int {
+    if (q < n_low) return q;                       // 0..i-1, then i (D1)
+    return diag_tiles ? q - 1 : q + 1;             // i (D2), i+1.. | i+1..
+  };
+
+  if (warp == 0) {
+    // =========================== producer (one lane) ===========================
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_vp);
+      tma_prefetch_desc(&tm_dv);
+      uint32_t g = 0;      // tiles loaded so far
+      uint32_t swaps = 0;  // loads of the A buffer so far
+      bool alive = true;
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_empty[slot], ((it >> 1) & 1) ^ 1, cta_abort, ctl, limit, -1, -1, DK_TK_EMPTY)) break;
+        const int ticket = atomicAdd(&ctl->ticket, 1);
+        s.tk_slot[slot] = ticket;
+        mbar_arrive(&s.tk_full[slot]);
+        int chain, i, n, n_low;
+        if (!item_geometry(ticket, chain, i, n, n_low)) break;
+        const int b = chain / H, h = chain % H;
+        if (!wait_barrier(&s.ki_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_KI_FREE)) break;
+        mbar_expect_tx(&s.ki_full, kTileBytes);
+        tma_load_4d(s.ki, &tm_k, &s.ki_full, 0, i * kBlock, h, b);
+        tma_load_4d(s.ki + kHalfBytes, &tm_k, &s.ki_full, 64, i * kBlock, h, b);
+        // A buffer: dV_i for the lower tiles (skipped when there are none), V'_i for the upper tiles
+        auto load_a = [&](const CUtensorMap* tm) -> bool {
+          if (!wait_barrier(&s.ai_free, (swaps & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_AI_FREE)) return false;
+          mbar_expect_tx(&s.ai_full, kTileBytes);
+          tma_load_4d(s.ai, tm, &s.ai_full, 0, i * kBlock, h, b);
+          tma_load_4d(s.ai + kHalfBytes, tm, &s.ai_full, 64, i * kBlock, h, b);
+          ++swaps;
+          return true;
+        };
+        if (n_low > 0 && !load_a(&tm_dv)) break;
+        for (int q = 0; q < n && alive; ++q) {
+          if (q == n_low && n_low < n) {
+            if (!load_a(&tm_vp)) { alive = false; break; }
+          }
+          const int j = tile_j(i, n_low, q);
+          const uint32_t gq = g + q;
+          const int ks = gq % 3, zs = gq & 1;
+          if (!wait_barrier(&s.k_empty[ks], ((gq / 3) & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_K_EMPTY)) {
+            alive = false;
+            break;
+          }
+          mbar_expect_tx(&s.k_full[ks], kTileBytes);
+          tma_load_4d(s.kring[ks], &tm_k, &s.k_full[ks], 0, j * kBlock, h, b);
+          tma_load_4d(s.kring[ks] + kHalfBytes, &tm_k, &s.k_full[ks], 64, j * kBlock, h, b);
+          if (!wait_barrier(&s.z_empty[zs], ((gq >> 1) & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_Z_EMPTY)) {
+            alive = false;
+            break;
+          }
+          const CUtensorMap* tz = (q < n_low) ? &tm_vp : &tm_dv;
+          mbar_expect_tx(&s.z_full[zs], kTileBytes);
+          tma_load_4d(s.zring[zs], tz, &s.z_full[zs], 0, j * kBlock, h, b);
+          tma_load_4d(s.zring[zs] + kHalfBytes, tz, &s.z_full[zs], 64, j * kBlock, h, b);
+        }
+        g += n;
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer (one lane) ===========================
+    if (lane == 0) {
+      constexpr int fmt = kBf16 ? 1 : 0;
+      constexpr uint32_t idesc_kk = umma_idesc(fmt, 0, 0, 128, 128);   // S and G: both operands K-major
+      constexpr uint32_t idesc_wk = umma_idesc(fmt, 0, 1, 128, 128);   // ACC += W K_j: B rows = k
+      const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
+      const uint64_t d_ai = umma_smem_desc(smem_u32(s.ai), 16, 1024);
+      uint64_t d_kr[3], d_kr_mn[3], d_zr[2];
+      for (int i = 0; i < 3; ++i) {
+        d_kr[i] = umma_smem_desc(smem_u32(s.kring[i]), 16, 1024);
+        d_kr_mn[i] = umma_smem_desc(smem_u32(s.kring[i]), kHalfBytes, 1024);
+      }
+      for (int i = 0; i < 2; ++i) d_zr[i] = umma_smem_desc(smem_u32(s.zring[i]), 16, 1024);
+      uint32_t g = 0, swaps = 0;
+      bool alive = true;
+      int chain = -1, i = -1, n = 0, n_low = 0;
+      auto issue_s = [&](uint32_t gq) -> bool {
+        const int ks = gq % 3;
+        if (!wait_barrier(&s.k_full[ks], (gq / 3) & 1, cta_abort, ctl, limit, chain, i, DK_K_FULL)) return false;
+        tc_fence_after_sync();
+        const uint32_t dst = tmem + ((gq & 1) ? kDkS1 : kDkS0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(dst, desc_advance(d_ki, off), desc_advance(d_kr[ks], off), idesc_kk, k ? 1u : 0u);
+        }
+        umma_commit(&s.s_full[gq & 1]);
+        return true;
+      };
+      auto issue_g = [&](uint32_t gq, int q) -> bool {
+        // the A buffer changes from dV_i to V'_i at q == n_low; wait for the load that serves tile q
+        if (q == 0 && n_low > 0) {
+          if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) return false;
+          ++swaps;
+        }
+        if (q == n_low && n_low < n) {
+          if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) return false;
+          ++swaps;
+        }
+        const int zs = gq & 1;
+        if (!wait_barrier(&s.z_full[zs], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_Z_FULL)) return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(tmem + kDkG, desc_advance(d_ai, off), desc_advance(d_zr[zs], off), idesc_kk, k ? 1u : 0u);
+        }
+        umma_commit(&s.z_empty[zs]);
+        umma_commit(&s.g_full);
+        // last lower tile (or last tile): the A buffer may be overwritten once this product is done
+        if (q == n_low - 1 || q == n - 1) umma_commit(&s.ai_free);
+        return true;
+      };
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, DK_TK_FULL)) break;
+        const int ticket = s.tk_slot[slot];
+        mbar_arrive(&s.tk_empty[slot]);
+        if (!item_geometry(ticket, chain, i, n, n_low)) break;
+        if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, DK_KI_FULL)) break;
+        tc_fence_after_sync();
+        if (n > 0) {
+          if (!issue_s(g) || !issue_g(g, 0)) break;
+        }
+        for (int q = 0; q < n; ++q) {
+          const uint32_t gq = g + q;
+          if (q + 1 < n && !issue_s(gq + 1)) { alive = false; break; }
+          // W(q) written (and G read) by all 256 threads
+          if (!wait_barrier(&s.w_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_W_FULL)) { alive = false; break; }
+          tc_fence_after_sync();
+          if (q + 1 < n && !issue_g(gq + 1, q + 1)) { alive = false; break; }
+          if (q == 0 &&
+              !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_ACC_FREE)) {
+            alive = false;
+            break;
+          }
+          const int ks = gq % 3;
+          const uint32_t w_tmem = tmem + ((gq & 1) ? kDkS1 : kDkS0);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            // W columns: k-steps 0-3 packed at columns 0-31, k-steps 4-7 at columns 64-95 of the S buffer
+            const uint32_t a_col = (k < 4) ? k * 8 : 64 + (k - 4) * 8;
+            umma_ts(tmem + kDkAcc, w_tmem + a_col, desc_advance(d_kr_mn[ks], k * 2048), idesc_wk,
+                    (q | k) ? 1u : 0u);
+          }
+          umma_commit(&s.k_empty[ks]);
+        }
+        if (!alive) break;
+        g += n;
+        // an item without tiles must not run ahead of the epilogue that still owns the previous phase
+        if (n == 0 && !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_ACC_FREE)) break;
+        umma_commit(&s.acc_full);
+        umma_commit(&s.ki_free);
+      }
+    }
+  } else if (warp >= 4) {
+    // =========================== W = -exp(S) o G, then the dK epilogue ===========================
+    const int wg = (warp - 4) >> 2;                  // column half: 64*wg .. 64*wg+63
+    const int row = ((warp & 3) << 5) + lane;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    uint32_t g = 0;
+    bool alive = true;
+    for (int it = 0; alive; ++it) {
+      const int slot = it & 1;
+      if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, DK_TK_FULL)) break;
+      const int ticket = s.tk_slot[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.tk_empty[slot]);
+      int chain, i, n, n_low;
+      if (!item_geometry(ticket, chain, i, n, n_low)) break;
+      const int b = chain / H, h = chain % H;
+      for (int q = 0; q < n; ++q) {
+        const uint32_t gq = g + q;
+        if (!wait_barrier(&s.s_full[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_S_FULL) ||
+            !wait_barrier(&s.g_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_G_FULL)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // diagonal tiles keep c <= r (D1, the last lower tile) or c >= r (D2, the first upper tile)
+        const int mask_mode = !diag_tiles ? 0 : (q == n_low - 1 ? 1 : (q == n_low ? 2 : 0));
+        const uint32_t s_tmem = lane_base + ((gq & 1) ? kDkS1 : kDkS0) + wg * 64;
+        const uint32_t g_tmem = lane_base + kDkG + wg * 64;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sv[32], gv[32];
+          tmem_ld32(s_tmem + c * 32, sv);
+          tmem_ld32(g_tmem + c * 32, gv);
+          tmem_wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float w0 = -ex2_approx(__uint_as_float(sv[2 * e]) * kLog2e) * __uint_as_float(gv[2 * e]);
+            float w1 = -ex2_approx(__uint_as_float(sv[2 * e + 1]) * kLog2e) * __uint_as_float(gv[2 * e + 1]);
+            if (mask_mode) {
+              const int col = wg * 64 + c * 32 + 2 * e;
+              const bool keep0 = (mask_mode == 1) ? (col <= row) : (col >= row);
+              const bool keep1 = (mask_mode == 1) ? (col + 1 <= row) : (col + 1 >= row);
+              w0 = keep0 ? w0 : 0.f;
+              w1 = keep1 ? w1 : 0.f;
+            }
+            pk[e] = pack2<kBf16>(w0, w1);
+          }
+          tmem_st16(s_tmem + c * 16, pk);   // this group's W half sits at columns 64*wg .. 64*wg+31
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&s.w_full);
+      }
+      if (!alive) break;
+      g += n;
+
+      // ---- epilogue: dK_i columns 64*wg .. +63 ----
+      if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, DK_ACC_FULL)) break;
+      tc_fence_after_sync();
+      typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
+      elem_t* out_row = reinterpret_cast<elem_t*>(args.dk) + (long long)b * args.dk_strides.b +
+                        (long long)(i * kBlock + row) * args.dk_strides.n + (long long)h * args.dk_strides.h + wg * 64;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t v[32];
+        if (n > 0) {
+          tmem_ld32(lane_base + kDkAcc + wg * 64 + cc * 32, v);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = 0u;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            o[e] = pack2<kBf16>(__uint_as_float(v[c * 8 + 2 * e]), __uint_as_float(v[c * 8 + 2 * e + 1]));
+          *reinterpret_cast<uint4*>(out_row + cc * 32 + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&s.acc_free);
+    }
+  }
+
+  if (s.abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    if (tid == 0) report_error(ctl, kErrAborted, -1, -1, blockIdx.x, 0);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+size_t dk_smem_bytes() { return sizeof(DkSmem) + 1024; }
+
+cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,
+                      const DkArgs& args, int grid, cudaStream_t stream) {
+  cudaError_t e;
+  if (bf16) {
+    e = cudaFuncSetAttribute(dk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dk_smem_bytes());
+    if (e != cudaSuccess) return e;
+    dk_kernel<true><<<grid, kDkThreads, dk_smem_bytes(), stream>>>(tm_k, tm_vp, tm_dv, args);
+  } else {
+    e = cudaFuncSetAttribute(dk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dk_smem_bytes());
+    if (e != cudaSuccess) return e;
+    dk_kernel<false><<<grid, kDkThreads, dk_smem_bytes(), stream>>>(tm_k, tm_vp, tm_dv, args);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace lucid

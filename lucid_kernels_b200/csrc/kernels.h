@@ -1,0 +1,40 @@
+// Argument blocks and host launchers of the three kernels (definitions in solve.cu, diag_prep.cu, dk.cu).
+#pragma once
+#include "common.cuh"
+
+namespace lucid {
+
+struct SolveArgs {
+  void* out;              // Y (V' or dV), written with plain stores, streamed back through a tensor map
+  Strides out_strides;
+  const float* lam_inv;   // (C, T, 128) exp(-|k_r|^2)
+  int* flags;             // (C, T)
+  Control* ctl;
+  long long* timestamps;  // (C, T, 8) or null
+  Problem p;
+};
+
+struct PrepArgs {
+  void* x;          // (C*T, 128, 128) 16-bit
+  float* lam_inv;   // (C*T, 128)
+  Control* ctl;
+  int T, H;
+  unsigned long long wait_ns;
+};
+
+struct DkArgs {
+  void* dk;
+  Strides dk_strides;
+  Control* ctl;
+  Problem p;
+};
+
+cudaError_t launch_solve(bool bf16, bool reverse, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
+                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const SolveArgs& args, int grid,
+                         cudaStream_t stream);
+cudaError_t launch_diag_prep(bool bf16, const CUtensorMap& tm_k, const PrepArgs& args, int nblocks,
+                             cudaStream_t stream);
+cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,
+                      const DkArgs& args, int grid, cudaStream_t stream);
+
+}  // namespace lucid

@@ -1,0 +1,502 @@
+// Block-triangular substitution on sm_100a: the forward solve V' = L^-1 V and, with kReverse, the
+// transposed solve dV = L^-T dV' of the backward pass.  Replaces the reference's ForwardSubSm90
+// (lucid_kernels/cute/forward_sub_fwd.py:47-841) and the dV part of BackwardSubSm90
+// (lucid_kernels/cute/forward_sub_bwd.py:1053-1107).
+//
+// One persistent CTA per SM takes row-blocks (chain, i) from a global ticket counter in dependency
+// order.  For every earlier block j of the chain it computes S = K_i K_j^T (tcgen05, both operands
+// from shared memory), P = exp(S) on the TMEM -> register path, and ACC += P * Y_j with P fed back
+// from TMEM (Y = V' forward, dV reverse).  The row-block then forms rhs = Y_in_i - ACC, applies the
+// unit-triangular inverse X_i (precomputed by diag_prep.cu) as one more MMA together with the row
+// scaling exp(-|k_r|^2), stores Y_i and publishes flag[chain][i] with release semantics.  Consumers
+// acquire the flag before their TMA load of Y_i.
+//
+// Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 MMA issuer
+// and TMEM owner, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warps 4-7 / 8-11 two
+// exp groups that alternate over the S buffers and share the epilogue (64 columns each).
+#include <type_traits>
+#include "kernels.h"
+
+namespace lucid {
+
+struct SolveSmem {
+  alignas(1024) uint8_t ki[kTileBytes];        // K_i: two 64-column panels, 128B-swizzled
+  alignas(1024) uint8_t x[kTileBytes];         // X_i, same layout
+  alignas(1024) uint8_t rhs[kTileBytes];       // V_i (then rhs) as [row][64-col panel] panels
+  alignas(1024) uint8_t kring[4][kHalfBytes];  // K_j panels (64 columns of d x 128 rows)
+  alignas(1024) uint8_t vring[4][kHalfBytes];  // Y_j row halves (2 panels x 64 rows x 64 columns)
+  alignas(8) uint64_t k_full[4];
+  uint64_t k_empty[4], v_full[4], v_empty[4];
+  uint64_t ki_full, ki_free, x_full, vi_full, xr_free;
+  uint64_t s_full[2], p_full[2];
+  uint64_t acc_full, acc_free, rhs_full, out_full, pub;
+  uint64_t tk_full[2], tk_empty[2];
+  int tk_slot[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+enum SolveBar : int {
+  BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
+  BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
+  BAR_TK_EMPTY, BAR_PUB
+};
+
+constexpr int kSolveThreads = 384;
+constexpr int kTmemS0 = 0, kTmemS1 = 128, kTmemAcc = 256, kTmemOut = 384;
+
+template <bool kBf16, bool kReverse>
+__global__ void __launch_bounds__(kSolveThreads, 1)
+solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
+             const __grid_constant__ CUtensorMap tm_in,    // V (or dV'), box 64 x 128
+             const __grid_constant__ CUtensorMap tm_out,   // Y, box 64 x 64
+             const __grid_constant__ CUtensorMap tm_x,     // X workspace (2D), box 64 x 128
+             const SolveArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  SolveSmem& s = *reinterpret_cast<SolveSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const Problem& P = args.p;
+  Control* ctl = args.ctl;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int T = P.T, H = P.H;
+  const unsigned long long limit = P.wait_ns;
+  volatile int* cta_abort = &s.abort_flag;
+
+  if (tid == 0) {
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&s.k_full[i], 1);
+      mbar_init(&s.k_empty[i], 1);
+      mbar_init(&s.v_full[i], 1);
+      mbar_init(&s.v_empty[i], 1);
+    }
+    mbar_init(&s.ki_full, 1);
+    mbar_init(&s.ki_free, 1);
+    mbar_init(&s.x_full, 1);
+    mbar_init(&s.vi_full, 1);
+    mbar_init(&s.xr_free, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.p_full[i], 128);
+      mbar_init(&s.tk_full[i], 1);
+      mbar_init(&s.tk_empty[i], 10);
+    }
+    mbar_init(&s.acc_full, 1);
+    mbar_init(&s.acc_free, 256);
+    mbar_init(&s.rhs_full, 256);
+    mbar_init(&s.out_full, 1);
+    mbar_init(&s.pub, 256);
+    s.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+
+  // Every role walks the same sequence of items; `it` counts items, `g` counts (i, j) tiles and `u`
+  // half-tiles, all per CTA, so that ring stages and barrier phases agree between roles.
+  auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& jfirst) -> bool {
+    int step;
+    if (!decode_ticket(ticket, P.C, T, P.group, chain, step)) return false;
+    if (kReverse) {
+      i = T - 1 - step;
+      n = step;           // blocks i+1 .. T-1, visited from T-1 down to i+1
+      jfirst = T - 1;
+    } else {
+      i = step;
+      n = (P.window > 0) ? min(step, P.window) : step;
+      jfirst = i - n;     // visited upward to i-1
+    }
+    return true;
+  };
+  auto tile_j = [&](int jfirst, int q) -> int { return kReverse ? jfirst - q : jfirst + q; };
+
+  if (warp == 0) {
+    // =========================== K producer (one lane) ===========================
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_x);
+      uint32_t u = 0;
+      bool alive = true;
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_empty[slot], ((it >> 1) & 1) ^ 1, cta_abort, ctl, limit, -1, -1, BAR_TK_EMPTY)) break;
+        const int ticket = atomicAdd(&ctl->ticket, 1);
+        s.tk_slot[slot] = ticket;
+        mbar_arrive(&s.tk_full[slot]);
+        int chain, i, n, jfirst;
+        if (!item_geometry(ticket, chain, i, n, jfirst)) break;
+        const int b = chain / H, h = chain % H;
+        // K_i once the previous item's S products have drained
+        if (!wait_barrier(&s.ki_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_KI_FREE)) break;
+        mbar_expect_tx(&s.ki_full, kTileBytes);
+        tma_load_4d(s.ki, &tm_k, &s.ki_full, 0, i * kBlock, h, b);
+        tma_load_4d(s.ki + kHalfBytes, &tm_k, &s.ki_full, 64, i * kBlock, h, b);
+        bool x_loaded = !P.use_diag;
+        for (int q = 0; q < n && alive; ++q) {
+          const int j = tile_j(jfirst, q);
+          for (int half = 0; half < 2; ++half, ++u) {
+            const int st = u & 3;
+            if (!wait_barrier(&s.k_empty[st], ((u >> 2) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_K_EMPTY)) {
+              alive = false;
+              break;
+            }
+            mbar_expect_tx(&s.k_full[st], kHalfBytes);
+            tma_load_4d(s.kring[st], &tm_k, &s.k_full[st], 64 * half, j * kBlock, h, b);
+          }
+          if (alive && !x_loaded && mbar_try_wait(&s.xr_free, (it & 1) ^ 1)) {
+            mbar_expect_tx(&s.x_full, kTileBytes);
+            tma_load_2d(s.x, &tm_x, &s.x_full, 0, (chain * T + i) * kBlock);
+            tma_load_2d(s.x + kHalfBytes, &tm_x, &s.x_full, 64, (chain * T + i) * kBlock);
+            x_loaded = true;
+          }
+        }
+        if (alive && !x_loaded) {
+          if (!wait_barrier(&s.xr_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_XR_FREE)) break;
+          mbar_expect_tx(&s.x_full, kTileBytes);
+          tma_load_2d(s.x, &tm_x, &s.x_full, 0, (chain * T + i) * kBlock);
+          tma_load_2d(s.x + kHalfBytes, &tm_x, &s.x_full, 64, (chain * T + i) * kBlock);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // =========================== Y producer (one lane) ===========================
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_in);
+      tma_prefetch_desc(&tm_out);
+      uint32_t u = 0;
+      bool alive = true;
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, BAR_TK_FULL)) break;
+        const int ticket = s.tk_slot[slot];
+        mbar_arrive(&s.tk_empty[slot]);
+        int chain, i, n, jfirst;
+        if (!item_geometry(ticket, chain, i, n, jfirst)) break;
+        const int b = chain / H, h = chain % H;
+        // This row-block's own right-hand side goes into the rhs buffer as soon as the previous
+        // item's diagonal product has released it; the ring loads below do not wait for that.
+        bool vi_loaded = false;
+        auto load_vi = [&]() {
+          mbar_expect_tx(&s.vi_full, kTileBytes);
+          tma_load_4d(s.rhs, &tm_in, &s.vi_full, 0, i * kBlock, h, b);
+          tma_load_4d(s.rhs + kHalfBytes, &tm_in, &s.vi_full, 64, i * kBlock, h, b);
+          vi_loaded = true;
+        };
+        unsigned long long waited = 0;
+        for (int q = 0; q < n && alive; ++q) {
+          const int j = tile_j(jfirst, q);
+          if (!vi_loaded && mbar_try_wait(&s.xr_free, (it & 1) ^ 1)) load_vi();
+          if (!P.no_sync) {
+            if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j,
+                           P.instrument ? &waited : nullptr)) {
+              alive = false;
+              break;
+            }
+            fence_proxy_async_all();   // flag acquired in the generic proxy; the tile is read by TMA
+          }
+          for (int half = 0; half < 2; ++half, ++u) {
+            const int st = u & 3;
+            if (!wait_barrier(&s.v_empty[st], ((u >> 2) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_V_EMPTY)) {
+              alive = false;
+              break;
+            }
+            mbar_expect_tx(&s.v_full[st], kHalfBytes);
+            tma_load_4d(s.vring[st], &tm_out, &s.v_full[st], 0, j * kBlock + 64 * half, h, b);
+            tma_load_4d(s.vring[st] + 8192, &tm_out, &s.v_full[st], 64, j * kBlock + 64 * half, h, b);
+          }
+        }
+        if (alive && !vi_loaded) {
+          if (!wait_barrier(&s.xr_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_XR_FREE)) break;
+          load_vi();
+        }
+        if (P.instrument && args.timestamps) args.timestamps[(chain * T + i) * 8 + 3] = (long long)waited;
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer (one lane) ===========================
+    if (lane == 0) {
+      constexpr int fmt = kBf16 ? 1 : 0;
+      constexpr uint32_t idesc_s = umma_idesc(fmt, 0, 0, 128, 128);    // S = K_i K_j^T
+      constexpr uint32_t idesc_pv = umma_idesc(fmt, 0, 1, 128, 128);   // ACC += P Y_j   (B: rows = k)
+      constexpr uint32_t idesc_out = umma_idesc(fmt, kReverse ? 1 : 0, 1, 128, 128);  // OUT = X(^T) rhs
+      const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
+      const uint64_t d_x = kReverse ? umma_smem_desc(smem_u32(s.x), kHalfBytes, 1024)
+                                    : umma_smem_desc(smem_u32(s.x), 16, 1024);
+      const uint64_t d_rhs = umma_smem_desc(smem_u32(s.rhs), kHalfBytes, 1024);
+      uint64_t d_kr[4], d_vr[4];
+      for (int i = 0; i < 4; ++i) {
+        d_kr[i] = umma_smem_desc(smem_u32(s.kring[i]), 16, 1024);
+        d_vr[i] = umma_smem_desc(smem_u32(s.vring[i]), 8192, 1024);
+      }
+      uint32_t g = 0;   // tiles issued so far (S buffer = g & 1)
+      bool alive = true;
+      auto issue_s = [&](uint32_t gq) -> bool {
+        // S[gq & 1] = K_i K_j^T, two K panels of four k-steps each
+        const uint32_t dst = tmem + ((gq & 1) ? kTmemS1 : kTmemS0);
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t u = gq * 2 + half;
+          const int st = u & 3;
+          if (!wait_barrier(&s.k_full[st], (u >> 2) & 1, cta_abort, ctl, limit, -1, -1, BAR_K_FULL)) return false;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            umma_ss(dst, desc_advance(d_ki, half * kHalfBytes + kk * 32), desc_advance(d_kr[st], kk * 32), idesc_s,
+                    (half | kk) ? 1u : 0u);
+          }
+          umma_commit(&s.k_empty[st]);
+        }
+        umma_commit(&s.s_full[gq & 1]);
+        return true;
+      };
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, BAR_TK_FULL)) break;
+        const int ticket = s.tk_slot[slot];
+        mbar_arrive(&s.tk_empty[slot]);
+        int chain, i, n, jfirst;
+        if (!item_geometry(ticket, chain, i, n, jfirst)) break;
+        if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_KI_FULL)) break;
+        tc_fence_after_sync();
+        if (n > 0 && !issue_s(g)) break;
+        for (int q = 0; q < n; ++q) {
+          const uint32_t gq = g + q;
+          if (q + 1 < n) {
+            if (!issue_s(gq + 1)) { alive = false; break; }
+          } else {
+            umma_commit(&s.ki_free);   // every S product of this item has been issued
+          }
+          if (!wait_barrier(&s.p_full[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) {
+            alive = false;
+            break;
+          }
+          if (q == 0 &&
+              !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FREE)) {
+            alive = false;
+            break;
+          }
+          const uint32_t p_tmem = tmem + ((gq & 1) ? kTmemS1 : kTmemS0);
+          for (int half = 0; half < 2 && alive; ++half) {
+            const uint32_t u = gq * 2 + half;
+            const int st = u & 3;
+            if (!wait_barrier(&s.v_full[st], (u >> 2) & 1, cta_abort, ctl, limit, chain, i, BAR_V_FULL)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              umma_ts(tmem + kTmemAcc, p_tmem + (half * 4 + kk) * 8, desc_advance(d_vr[st], kk * 2048), idesc_pv,
+                      (q | half | kk) ? 1u : 0u);
+            }
+            umma_commit(&s.v_empty[st]);
+          }
+        }
+        if (!alive) break;
+        g += n;
+        if (n == 0) {
+          mbar_arrive(&s.ki_free);   // nothing read K_i
+        }
+        umma_commit(&s.acc_full);
+        // diagonal step
+        if (!wait_barrier(&s.rhs_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_RHS_FULL)) break;
+        tc_fence_after_sync();
+        if (P.use_diag) {
+          if (!wait_barrier(&s.x_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_X_FULL)) break;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint64_t da = kReverse ? desc_advance(d_x, k * 2048)
+                                         : desc_advance(d_x, (k >> 2) * kHalfBytes + (k & 3) * 32);
+            umma_ss(tmem + kTmemOut, da, desc_advance(d_rhs, k * 2048), idesc_out, k ? 1u : 0u);
+          }
+          umma_commit(&s.out_full);
+          umma_commit(&s.xr_free);
+        } else {
+          mbar_arrive(&s.xr_free);
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // =========================== exp groups + epilogue ===========================
+    const int wg = (warp - 4) >> 2;                  // 0 or 1: S buffer parity, epilogue column panel
+    const int row = ((warp & 3) << 5) + lane;        // TMEM lane == row of the block
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t s_tmem = lane_base + (wg ? kTmemS1 : kTmemS0);
+    uint32_t g = 0;
+    bool alive = true;
+    for (int it = 0; alive; ++it) {
+      const int slot = it & 1;
+      if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, BAR_TK_FULL)) break;
+      const int ticket = s.tk_slot[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.tk_empty[slot]);
+      int chain, i, n, jfirst;
+      if (!item_geometry(ticket, chain, i, n, jfirst)) break;
+      const int b = chain / H, h = chain % H;
+      long long t_start = 0;
+      if (P.instrument && tid == 128) t_start = (long long)globaltimer_ns();
+      const float lam = P.use_diag ? args.lam_inv[(chain * T + i) * kBlock + row] : 1.0f;
+
+      // ---- P = exp(S) for the tiles of my parity ----
+      for (int q = 0; q < n; ++q) {
+        const uint32_t gq = g + q;
+        if ((gq & 1) != (uint32_t)wg) continue;
+        if (!wait_barrier(&s.s_full[wg], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(s_tmem + c * 32, v);
+          tmem_wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float e0 = ex2_approx(__uint_as_float(v[2 * e]) * kLog2e);
+            const float e1 = ex2_approx(__uint_as_float(v[2 * e + 1]) * kLog2e);
+            pk[e] = pack2<kBf16>(e0, e1);
+          }
+          tmem_st16(s_tmem + c * 16, pk);   // P overwrites the S columns already consumed
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&s.p_full[wg]);
+      }
+      if (!alive) break;
+      g += n;
+
+      // ---- epilogue: this group owns output columns 64*wg .. 64*wg+63 ----
+      float acc[64];
+      if (n > 0) {
+        if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FULL)) break;
+        tc_fence_after_sync();
+        uint32_t v[32];
+        tmem_ld32(lane_base + kTmemAcc + wg * 64, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(v[e]);
+        tmem_ld32(lane_base + kTmemAcc + wg * 64 + 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[32 + e] = __uint_as_float(v[e]);
+      } else {
+        if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FULL)) break;
+#pragma unroll
+        for (int e = 0; e < 64; ++e) acc[e] = 0.f;
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&s.acc_free);
+      long long t_loop = 0;
+      if (P.instrument && tid == 128) t_loop = (long long)globaltimer_ns();
+
+      if (!wait_barrier(&s.vi_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_VI_FULL)) break;
+      uint8_t* panel = s.rhs + wg * kHalfBytes;
+      const float pre = (P.use_diag && !kReverse) ? lam : 1.0f;   // forward: rows scaled before X
+      const float post = (P.use_diag && kReverse) ? lam : 1.0f;   // reverse: rows scaled after X^T
+      typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
+      elem_t* out_row = reinterpret_cast<elem_t*>(args.out) + (long long)b * args.out_strides.b +
+                        (long long)(i * kBlock + row) * args.out_strides.n + (long long)h * args.out_strides.h +
+                        wg * 64;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4* p = reinterpret_cast<uint4*>(panel + sw128_off(row, c));
+        uint4 w = *p;
+        uint32_t in[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack2<kBf16>(in[e]);
+          const float r0 = (f.x - acc[c * 8 + 2 * e]) * pre;
+          const float r1 = (f.y - acc[c * 8 + 2 * e + 1]) * pre;
+          o[e] = pack2<kBf16>(r0, r1);
+        }
+        const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+        if (P.use_diag) *p = ov;
+        else *reinterpret_cast<uint4*>(out_row + c * 8) = ov;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&s.rhs_full);
+
+      if (P.use_diag) {
+        if (!wait_barrier(&s.out_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_OUT_FULL)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t v[32];
+          tmem_ld32(lane_base + kTmemOut + wg * 64 + cc * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              o[e] = pack2<kBf16>(__uint_as_float(v[c * 8 + 2 * e]) * post, __uint_as_float(v[c * 8 + 2 * e + 1]) * post);
+            }
+            *reinterpret_cast<uint4*>(out_row + cc * 32 + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+      // ---- publish: all 256 epilogue threads' stores, then one release store of the flag ----
+      __threadfence();
+      mbar_arrive(&s.pub);
+      if (tid == 128) {
+        if (!wait_barrier(&s.pub, it & 1, cta_abort, ctl, limit, chain, i, BAR_PUB)) break;
+        fence_proxy_async_all();
+        st_release_gpu(args.flags + chain * T + i, 1);
+        if (P.instrument && args.timestamps) {
+          long long* ts = args.timestamps + (long long)(chain * T + i) * 8;
+          ts[0] = t_start;
+          ts[1] = t_loop;
+          ts[2] = (long long)globaltimer_ns();
+          ts[4] = blockIdx.x;
+          ts[5] = n;
+        }
+      }
+    }
+  }
+
+  // teardown: everybody meets here, also after an abort
+  if (s.abort_flag) {
+    // give copies and MMAs still in flight time to land before shared memory and TMEM are released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    if (tid == 0) report_error(ctl, kErrAborted, -1, -1, blockIdx.x, 0);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host launcher
+// ---------------------------------------------------------------------------------------------
+size_t solve_smem_bytes() { return sizeof(SolveSmem) + 1024; }
+
+template <bool kBf16, bool kReverse>
+static cudaError_t launch_solve_t(const CUtensorMap& tm_k, const CUtensorMap& tm_in, const CUtensorMap& tm_out,
+                                  const CUtensorMap& tm_x, const SolveArgs& args, int grid, cudaStream_t stream) {
+  auto kern = solve_kernel<kBf16, kReverse>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem_bytes());
+  if (e != cudaSuccess) return e;
+  kern<<<grid, kSolveThreads, solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_solve(bool bf16, bool reverse, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
+                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const SolveArgs& args, int grid,
+                         cudaStream_t stream) {
+  if (bf16) {
+    return reverse ? launch_solve_t<true, true>(tm_k, tm_in, tm_out, tm_x, args, grid, stream)
+                   : launch_solve_t<true, false>(tm_k, tm_in, tm_out, tm_x, args, grid, stream);
+  }
+  return reverse ? launch_solve_t<false, true>(tm_k, tm_in, tm_out, tm_x, args, grid, stream)
+                 : launch_solve_t<false, false>(tm_k, tm_in, tm_out, tm_x, args, grid, stream);
+}
+
+}  // namespace lucid
