@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the LUCID forward substitution + backward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" = one forward solve (V') plus one backward pass (dV, dK) over the workload
+B=2, N=32768, H=8, d=128, bf16 (use_diag_solve, combined backward), on synthetic seeded inputs
+(K ~ N(0,1)*d^-1/4, V and dV' ~ N(0,1)).  With N > 1 ranks (torchrun, one process per GPU) the 16
+independent (batch, head) systems are sharded over the ranks; there is no collective on the data path.
+
+Prints ONE JSON line (rank 0).  `value` is whole-job algorithmic TFLOP/s with inputs resident in HBM;
+`e2e` is the same metric through the operator interface with host buffers (pinned host -> device copies
+of K, V, dV' and device -> host copies of V', dV, dK inside the timed region).
+
+`--impl reference` times the reference's own naive CPU path (dense L + torch.linalg.solve_triangular +
+autograd, fp32) on a bounded sample of the same workload, on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(B=2, N=32768, H=8, D=128)
+METRIC = "lucid_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+G = 2.0 * 128 ** 3
+
+
+def flops_split(nsys: int, N: int):
+    """Algorithmic flops of `nsys` systems: (forward, reverse solve, dK).  Per system and pair of
+    blocks: forward 2g (S, P V'), reverse solve 2g (S, P dV), dK 3g (G, W K_j, W^T K_i); per diagonal block
+    1.5g, 1.5g and 2g.  forward + reverse + dK = pairs*7g ... the backward total pairs*5g + T*3.5g counts the
+    S product once: the reverse solve is charged 2g and dK 3g."""
+    T = N // 128
+    pairs = T * (T - 1) / 2
+    fwd = nsys * (pairs * 2 * G + T * 1.5 * G)
+    rev = nsys * (pairs * 2 * G + T * 1.5 * G)
+    dk = nsys * (pairs * 3 * G + T * 2.0 * G)
+    return fwd, rev, dk
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(bf16_tflops=d["bf16_tflops"], bf16_tflops_sustained=d["bf16_tflops_sustained"],
+                    hbm_gbs=d["hbm_gbs"], source="measured")
+    return dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines]
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(smax) if smax else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU path (reference arm and cpu_baseline leg)
+# ------------------------------------------------------------------------------------------------
+def cpu_naive_sample(budget_s: float = 15.0):
+    """The reference's naive path (dense L + solve_triangular + autograd, fp32) on a bounded sample of
+    the workload: B=1, N=4096, H=2 of the same value distribution.  Returns TFLOP/s and a description."""
+    from oracle import lucid_oracle as orc
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    B, N, H = 1, 4096, 2
+    K, V, dVp = orc.make_inputs(B, N, H, dtype=torch.float32)
+    f, b = orc.algorithmic_flops(B, N, H)
+    times = []
+    t_begin = time.perf_counter()
+    orc.naive_cpu_fwd_bwd(K, V, dVp)  # warm-up
+    while len(times) < 3 or (time.perf_counter() - t_begin < budget_s and len(times) < 50):
+        t0 = time.perf_counter()
+        orc.naive_cpu_fwd_bwd(K, V, dVp)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > 2 * budget_s:
+            break
+    med = statistics.median(times)
+    return dict(value=(f + b) / med / 1e12, unit=UNIT, cores=cores, kind="port",
+                sample=f"dense L + solve_triangular + autograd fp32, B={B} N={N} H={H} (same distribution), "
+                       f"median of {len(times)} runs, {med * 1e3:.0f} ms each"), med
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    cb, med = cpu_naive_sample(budget_s=max(5.0, 4.0 * (args.steps + args.warmup)))
+    line = dict(impl="reference", metric=METRIC, value=cb["value"], unit=UNIT, n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=med * 1e3, higher_is_better=True, scaling="strong",
+                vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload="LUCID fwd+bwd B=2 N=32768 H=8 d=128 (bounded CPU sample, see cpu_baseline.sample)"),
+                cpu_baseline=cb,
+                e2e=dict(value=cb["value"], unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0, wall_s=time.perf_counter() - t0)
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--seqlen", type=int, default=WORKLOAD["N"], help="override N (parity/profiling runs only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch.distributed as dist
+    from oracle import lucid_oracle as orc  # input generator and the cpu_baseline leg only
+    from lucid_kernels_b200 import _cabi
+    from lucid_kernels_b200.cute import _forward_sub_fwd, _forward_sub_bwd
+    from lucid_kernels_b200.sharding import shard_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the product path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _cabi.load()
+
+    B, N, H, D = WORKLOAD["B"], args.seqlen, WORKLOAD["H"], WORKLOAD["D"]
+    nsys = B * H
+    lo, hi = shard_range(nsys, world, rank)
+    n_local = hi - lo
+    # each rank materialises only its own systems, as a (1, N, n_local, 128) BSHD tensor
+    K, V, dVp = orc.make_inputs(B, N, H, dtype=torch.bfloat16, hb_slice=(lo, hi))
+    Kh, Vh, Gh = K.pin_memory(), V.pin_memory(), dVp.pin_memory()
+    Kd, Vd, Gd = Kh.to(dev), Vh.to(dev), Gh.to(dev)
+    f_fwd, f_rev, f_dk = flops_split(nsys, N)
+    total_flops = f_fwd + f_rev + f_dk
+
+    def step():
+        vp = _forward_sub_fwd(Kd, Vd, use_diag_solve=True)
+        dv, dk = _forward_sub_bwd(Kd, vp, Gd, use_diag_solve=True, use_combined_kernel=True)
+        return vp, dv, dk
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events on the launching stream, per-kernel events inside ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    mk = lambda: torch.cuda.Event(enable_timing=True)
+    kern_ev = []
+    for _ in range(args.steps):
+        evs = [mk() for _ in range(7)]
+        for e in evs:
+            e.record()   # forces creation of the underlying handle
+        kern_ev.append(evs)
+    barrier()
+    ev0, ev1 = mk(), mk()
+    t_wall0 = time.time()
+    ev0.record()
+    for s in range(args.steps):
+        e = kern_ev[s]
+        lib.lucid_profile_next_call(e[0].cuda_event, e[1].cuda_event, e[2].cuda_event, None)
+        vp = _forward_sub_fwd(Kd, Vd, use_diag_solve=True)
+        lib.lucid_profile_next_call(e[3].cuda_event, e[4].cuda_event, e[5].cuda_event, e[6].cuda_event)
+        dv, dk = _forward_sub_bwd(Kd, vp, Gd, use_diag_solve=True, use_combined_kernel=True)
+    ev1.record()
+    barrier()
+    t_wall1 = time.time()
+    clocks = sampler.stop(t_wall0, t_wall1)
+    ms_total = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    # per-kernel averages (this rank)
+    def avg(i, j):
+        return sum(kern_ev[s][i].elapsed_time(kern_ev[s][j]) for s in range(args.steps)) / args.steps
+    k_ms = dict(fwd_prep=avg(0, 1), fwd_solve=avg(1, 2), bwd_prep=avg(3, 4), bwd_solve=avg(4, 5), bwd_dk=avg(5, 6))
+    st = _cabi.read_status(_cabi.workspace(dev, torch.cuda.current_stream().cuda_stream, 1, N, n_local),
+                           torch.cuda.current_stream().cuda_stream)
+    if st[0] != 0:
+        raise SystemExit(f"device-side error during the timed region: {st}")
+
+    # ---- e2e: host buffers in, host buffers out, through the operator interface ----
+    e2e = None
+    if not args.no_e2e:
+        outs_h = [torch.empty_like(Kh).pin_memory() for _ in range(3)]
+        def e2e_step():
+            kd = Kh.to(dev, non_blocking=True)
+            vd = Vh.to(dev, non_blocking=True)
+            gd = Gh.to(dev, non_blocking=True)
+            vp = _forward_sub_fwd(kd, vd, use_diag_solve=True)
+            dv, dk = _forward_sub_bwd(kd, vp, gd, use_diag_solve=True, use_combined_kernel=True)
+            outs_h[0].copy_(vp, non_blocking=True)
+            outs_h[1].copy_(dv, non_blocking=True)
+            outs_h[2].copy_(dk, non_blocking=True)
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        n_e2e = max(3, min(args.steps, 10))
+        a, b_ = mk(), mk()
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b_.record()
+        barrier()
+        te = torch.tensor([a.elapsed_time(b_)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        ms_e2e = float(te.item()) / n_e2e
+        nbytes = Kh.numel() * Kh.element_size()
+        e2e = dict(value=total_flops / (ms_e2e * 1e-3) / 1e12, unit=UNIT, ms_per_step=ms_e2e,
+                   h2d_bytes_per_step=3 * nbytes, d2h_bytes_per_step=3 * nbytes, steps=n_e2e)
+
+    if rank == 0:
+        peaks = load_peaks()
+        # dominant kernel = the dK kernel; roofline against the burst tensor peak
+        f_dk_local = f_dk * n_local / nsys
+        dk_tflops = f_dk_local / (k_ms["bwd_dk"] * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        roofline = dict(bound="tensor", kernel="dk_kernel", achieved=dk_tflops, peak=peak, unit="TFLOP/s",
+                        frac=dk_tflops / peak, traffic=None, peak_source=peaks["source"] + " (sustained)",
+                        per_kernel_ms=k_ms,
+                        per_kernel_tflops=dict(
+                            fwd_solve=f_fwd * n_local / nsys / (k_ms["fwd_solve"] * 1e-3) / 1e12,
+                            bwd_solve=f_rev * n_local / nsys / (k_ms["bwd_solve"] * 1e-3) / 1e12,
+                            bwd_dk=dk_tflops))
+        line = dict(metric=METRIC, value=total_flops / (ms_step * 1e-3) / 1e12, unit=UNIT, n_gpus=world,
+                    steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True,
+                    scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+                    config=dict(workload=f"LUCID fwd+bwd (V', dV, dK) B={B} N={N} H={H} d={D} bf16 BSHD, "
+                                         "use_diag_solve, combined backward",
+                                sharding=f"{nsys} (batch, head) systems over {world} rank(s), no collective",
+                                l2="inputs (3 x 128 MiB per step at N=32768) exceed the 126 MB L2; no flush",
+                                seed=0),
+                    frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (world * peaks["bf16_tflops"]),
+                    roofline=roofline, clocks=clocks, gpu_launches=5 * args.steps, e2e=e2e)
+        if not args.no_cpu_baseline and world >= 1:
+            cb, _ = cpu_naive_sample()
+            line["cpu_baseline"] = cb
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

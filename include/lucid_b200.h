@@ -83,6 +83,12 @@ const char* lucid_status_string(int code);
 /* Sets the time limit (nanoseconds) of every device-side wait; default 2e9. */
 void lucid_set_wait_limit_ns(uint64_t ns);
 
+/* Per-kernel timing for benchmarks: the NEXT lucid_fwd_sub / lucid_bwd_sub call records these
+ * cudaEvent_t handles on its stream (before the diagonal-prep kernel, after it, after the solve kernel,
+ * after the dK kernel); any of them may be NULL.  The handles are forgotten after that call.  Stands in
+ * for the reference's `instrument=True` compile flag (forward_sub_interface.py:62) at kernel granularity. */
+void lucid_profile_next_call(void* ev_begin, void* ev_after_prep, void* ev_after_solve, void* ev_after_dk);
+
 /* Offsets inside the workspace, for tools that read the instrumentation:
  * timestamps are int64[(B*H)][T][8] = {start, loop end, published, ns spent in flag waits, CTA, tiles}
  * (cf. the (T, 8) buffer of forward_sub_interface.py:103). */

@@ -9,6 +9,12 @@
 namespace lucid {
 
 static unsigned long long g_wait_ns = 2000000000ull;
+// optional per-kernel timing: events recorded around the kernels of the NEXT call, then forgotten
+static cudaEvent_t g_events[4] = {nullptr, nullptr, nullptr, nullptr};
+static long long* g_trace = nullptr;
+static inline void record_event(int i, cudaStream_t stream) {
+  if (g_events[i]) cudaEventRecord(g_events[i], stream);
+}
 
 // ---- workspace layout ----------------------------------------------------------------------
 //   [0, 256)            three Control blocks: 0 = diag prep, 1 = solve, 2 = dK
@@ -74,9 +80,9 @@ static int bshd_map(CUtensorMap* m, bool bf16, const void* p, const int64_t st[3
 
 static int auto_group(int C, int N, int requested) {
   if (requested > 0) return requested < C ? requested : C;
-  // K and Y of one chain take N * 512 bytes; keep the group's working set near half of a 126 MB L2
+  // K and Y of one chain take N * 512 bytes; keep the group within about one L2 (126 MB)
   const long long per_chain = (long long)N * 512;
-  long long g = (64ll << 20) / per_chain;
+  long long g = (128ll << 20) / per_chain;
   if (g < 1) g = 1;
   if (g > C) g = C;
   return (int)g;
@@ -115,6 +121,7 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
     if (make_tmap_16bit(&tm_x, bf16, ws + lay.x, 2, dims, str, 128)) return LUCID_E_TENSOR_MAP;
   }
   cudaError_t e;
+  record_event(0, stream);
   if (p.use_diag) {
     PrepArgs pa;
     pa.x = ws + lay.x;
@@ -125,6 +132,7 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
     pa.wait_ns = p.wait_ns;
     if ((e = launch_diag_prep(bf16, tm_k, pa, CT, stream)) != cudaSuccess) return (int)e;
   }
+  record_event(1, stream);
   SolveArgs sa;
   sa.out = out;
   sa.out_strides = Strides{outs[0], outs[1], outs[2]};
@@ -132,11 +140,13 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
   sa.flags = reinterpret_cast<int*>(ws + lay.flags);
   sa.ctl = ctl + 1;
   sa.timestamps = p.instrument ? reinterpret_cast<long long*>(ws + lay.ts) : nullptr;
+  sa.trace = g_trace;
   sa.p = p;
   const int sms = sm_count();
   if (sms <= 0) return LUCID_E_NO_DEVICE;
   const int grid = CT < sms ? CT : sms;
   if ((e = launch_solve(bf16, reverse, tm_k, tm_in, tm_out, tm_x, sa, grid, stream)) != cudaSuccess) return (int)e;
+  record_event(2, stream);
   return 0;
 }
 
@@ -158,6 +168,17 @@ size_t lucid_workspace_timestamps_offset(int B, int N, int H) {
 
 void lucid_set_wait_limit_ns(uint64_t ns) { g_wait_ns = ns; }
 
+#ifdef LUCID_TRACE
+void lucid_debug_set_trace(void* buf) { g_trace = static_cast<long long*>(buf); }
+#endif
+
+void lucid_profile_next_call(void* ev_begin, void* ev_after_prep, void* ev_after_solve, void* ev_after_dk) {
+  g_events[0] = static_cast<cudaEvent_t>(ev_begin);
+  g_events[1] = static_cast<cudaEvent_t>(ev_after_prep);
+  g_events[2] = static_cast<cudaEvent_t>(ev_after_solve);
+  g_events[3] = static_cast<cudaEvent_t>(ev_after_dk);
+}
+
 int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
                   const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D, int dtype,
                   int flags, int window_blocks, int chain_group, void* workspace, size_t workspace_bytes,
@@ -176,8 +197,10 @@ int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_s
   cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);   // control words + flags
   if (e != cudaSuccess) return (int)e;
   const Problem p = make_problem(B, N, H, flags, window_blocks, chain_group);
-  return run_solve(false, k, v, v_prime, k_strides, v_strides, vp_strides, p, dtype == LUCID_DTYPE_BF16, ws, lay,
-                   stream);
+  rc = run_solve(false, k, v, v_prime, k_strides, v_strides, vp_strides, p, dtype == LUCID_DTYPE_BF16, ws, lay,
+                 stream);
+  memset(g_events, 0, sizeof(g_events));
+  return rc;
 }
 
 int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void* dv, void* dk,
@@ -203,8 +226,10 @@ int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void
   if (e != cudaSuccess) return (int)e;
   const bool bf16 = dtype == LUCID_DTYPE_BF16;
   const Problem p = make_problem(B, N, H, flags, 0, chain_group);
-  if ((rc = run_solve(true, k, dv_prime, dv, k_strides, dvp_strides, dv_strides, p, bf16, ws, lay, stream)))
-    return rc;
+  rc = run_solve(true, k, dv_prime, dv, k_strides, dvp_strides, dv_strides, p, bf16, ws, lay, stream);
+  cudaEvent_t ev_dk = g_events[3];
+  memset(g_events, 0, sizeof(g_events));
+  if (rc) return rc;
   if (mode == LUCID_BWD_COMBINED) {
     CUtensorMap tm_k, tm_vp, tm_dv;
     if ((rc = bshd_map(&tm_k, bf16, k, k_strides, B, N, H, 128))) return rc;
@@ -214,12 +239,14 @@ int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void
     da.dk = dk;
     da.dk_strides = Strides{dk_strides[0], dk_strides[1], dk_strides[2]};
     da.ctl = reinterpret_cast<Control*>(ws) + 2;
+    da.trace = g_trace;
     da.p = p;
     const int sms = sm_count();
     if (sms <= 0) return LUCID_E_NO_DEVICE;
     const int CT = p.C * p.T;
     const int grid = CT < sms ? CT : sms;
     if ((e = launch_dk(bf16, tm_k, tm_vp, tm_dv, da, grid, stream)) != cudaSuccess) return (int)e;
+    if (ev_dk) cudaEventRecord(ev_dk, stream);
   }
   return 0;
 }

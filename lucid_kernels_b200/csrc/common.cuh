@@ -119,6 +119,23 @@ __device__ __forceinline__ bool decode_ticket(int t, int C, int T, int group, in
   return true;
 }
 
+// Event trace of one CTA (debugging builds only): role r appends {tag, q, clock} triples.
+#ifdef LUCID_TRACE
+constexpr int kTraceMax = 8192;
+#define LUCID_TR(buf, role, cnt, tag, q)                                              \
+  do {                                                                                \
+    if ((buf) != nullptr && blockIdx.x == 0 && (cnt) < kTraceMax) {                   \
+      long long* e_ = (buf) + ((long long)(role) * kTraceMax + (cnt)) * 3;            \
+      e_[0] = (tag);                                                                  \
+      e_[1] = (q);                                                                    \
+      e_[2] = clock64();                                                              \
+      ++(cnt);                                                                        \
+    }                                                                                 \
+  } while (0)
+#else
+#define LUCID_TR(buf, role, cnt, tag, q) do { } while (0)
+#endif
+
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -12,7 +12,9 @@
 // no flags, no ordering; a CTA owns row-block i and streams all T blocks j past it (T + 1 tiles).
 //
 // Warp roles (384 threads): warp 0 producer (tickets, K_i, A_i, K_j ring of 3, Z_j ring of 2), warp 1
-// MMA issuer and TMEM owner, warps 4-11 form W: both groups work on the same tile, 64 columns each.
+// issues the S and G products and owns TMEM, warp 3 issues the W*K_j products (two issuing warps so that
+// the waits of one overlap the MMAs of the other), warps 4-11 form W: both groups work on the same
+// tile, 64 columns each.
 #include <type_traits>
 #include "kernels.h"
 
@@ -26,7 +28,7 @@ struct DkSmem {
   alignas(8) uint64_t k_full[3];
   uint64_t k_empty[3], z_full[2], z_empty[2];
   uint64_t ki_full, ki_free, ai_full, ai_free;
-  uint64_t s_full[2], g_full, w_full;
+  uint64_t s_full[2], g_full, w_full, w_ready[2], sbuf_free[2];
   uint64_t acc_full, acc_free;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
@@ -36,7 +38,7 @@ struct DkSmem {
 
 enum DkBar : int {
   DK_K_FULL = 201, DK_K_EMPTY, DK_Z_FULL, DK_Z_EMPTY, DK_KI_FULL, DK_KI_FREE, DK_AI_FULL, DK_AI_FREE, DK_S_FULL,
-  DK_G_FULL, DK_W_FULL, DK_ACC_FULL, DK_ACC_FREE, DK_TK_FULL, DK_TK_EMPTY
+  DK_G_FULL, DK_W_FULL, DK_ACC_FULL, DK_ACC_FREE, DK_TK_FULL, DK_TK_EMPTY, DK_SBUF_FREE, DK_W_READY
 };
 
 constexpr int kDkThreads = 384;
@@ -68,8 +70,10 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
       mbar_init(&s.z_full[i], 1);
       mbar_init(&s.z_empty[i], 1);
       mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.sbuf_free[i], 1);
+      mbar_init(&s.w_ready[i], 256);
       mbar_init(&s.tk_full[i], 1);
-      mbar_init(&s.tk_empty[i], 9);
+      mbar_init(&s.tk_empty[i], 10);
     }
     mbar_init(&s.ki_full, 1);
     mbar_init(&s.ki_free, 1);
@@ -165,99 +169,148 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
       }
     }
   } else if (warp == 1) {
-    // =========================== MMA issuer (one lane) ===========================
-    if (lane == 0) {
+    // =========================== S and G issuer ===========================
+    // Warp-uniform control flow; one elected lane issues tcgen05 instructions and arrivals.
+    {
       constexpr int fmt = kBf16 ? 1 : 0;
       constexpr uint32_t idesc_kk = umma_idesc(fmt, 0, 0, 128, 128);   // S and G: both operands K-major
-      constexpr uint32_t idesc_wk = umma_idesc(fmt, 0, 1, 128, 128);   // ACC += W K_j: B rows = k
       const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
       const uint64_t d_ai = umma_smem_desc(smem_u32(s.ai), 16, 1024);
-      uint64_t d_kr[3], d_kr_mn[3], d_zr[2];
-      for (int i = 0; i < 3; ++i) {
-        d_kr[i] = umma_smem_desc(smem_u32(s.kring[i]), 16, 1024);
-        d_kr_mn[i] = umma_smem_desc(smem_u32(s.kring[i]), kHalfBytes, 1024);
-      }
-      for (int i = 0; i < 2; ++i) d_zr[i] = umma_smem_desc(smem_u32(s.zring[i]), 16, 1024);
+      const uint64_t d_kr0 = umma_smem_desc(smem_u32(s.kring[0]), 16, 1024);             // stage: + 32 KiB
+      const uint64_t d_zr0 = umma_smem_desc(smem_u32(s.zring[0]), 16, 1024);
       uint32_t g = 0, swaps = 0;
       bool alive = true;
+      int trc = 0;
+      (void)trc;
+      const bool leader = (lane == 0);
+      (void)leader;
       int chain = -1, i = -1, n = 0, n_low = 0;
       auto issue_s = [&](uint32_t gq) -> bool {
-        const int ks = gq % 3;
+        const uint32_t ks = gq % 3;
+        const uint32_t buf = gq & 1;
+        // W of two tiles ago lived in this buffer: its W*K_j product must have completed
+        if (!wait_barrier(&s.sbuf_free[buf], ((gq >> 1) & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_SBUF_FREE))
+          return false;
+        if (leader) LUCID_TR(args.trace, 2, trc, 29, gq);
         if (!wait_barrier(&s.k_full[ks], (gq / 3) & 1, cta_abort, ctl, limit, chain, i, DK_K_FULL)) return false;
         tc_fence_after_sync();
-        const uint32_t dst = tmem + ((gq & 1) ? kDkS1 : kDkS0);
+        if (leader) LUCID_TR(args.trace, 2, trc, 30, gq);
+        const uint32_t dst = tmem + (buf ? kDkS1 : kDkS0);
+        const uint64_t db = d_kr0 + ks * (kTileBytes >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(dst, desc_advance(d_ki, off), desc_advance(d_kr[ks], off), idesc_kk, k ? 1u : 0u);
+          const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+          umma_ss_w(dst, d_ki + off, db + off, idesc_kk, k ? 1u : 0u);
         }
-        umma_commit(&s.s_full[gq & 1]);
+        umma_commit_w(&s.s_full[buf]);
+        if (leader) LUCID_TR(args.trace, 2, trc, 31, gq);
         return true;
       };
       auto issue_g = [&](uint32_t gq, int q) -> bool {
         // the A buffer changes from dV_i to V'_i at q == n_low; wait for the load that serves tile q
-        if (q == 0 && n_low > 0) {
+        if ((q == 0 && n_low > 0) || (q == n_low && n_low < n)) {
           if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) return false;
           ++swaps;
         }
-        if (q == n_low && n_low < n) {
-          if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) return false;
-          ++swaps;
-        }
-        const int zs = gq & 1;
+        const uint32_t zs = gq & 1;
         if (!wait_barrier(&s.z_full[zs], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_Z_FULL)) return false;
         tc_fence_after_sync();
+        if (leader) LUCID_TR(args.trace, 2, trc, 32, gq);
+        const uint64_t db = d_zr0 + zs * (kTileBytes >> 4);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(tmem + kDkG, desc_advance(d_ai, off), desc_advance(d_zr[zs], off), idesc_kk, k ? 1u : 0u);
+          const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+          umma_ss_w(tmem + kDkG, d_ai + off, db + off, idesc_kk, k ? 1u : 0u);
         }
-        umma_commit(&s.z_empty[zs]);
-        umma_commit(&s.g_full);
+        umma_commit_w(&s.z_empty[zs]);
+        umma_commit_w(&s.g_full);
+        if (leader) LUCID_TR(args.trace, 2, trc, 33, gq);
         // last lower tile (or last tile): the A buffer may be overwritten once this product is done
-        if (q == n_low - 1 || q == n - 1) umma_commit(&s.ai_free);
+        if (q == n_low - 1 || q == n - 1) umma_commit_w(&s.ai_free);
         return true;
       };
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, DK_TK_FULL)) break;
         const int ticket = s.tk_slot[slot];
-        mbar_arrive(&s.tk_empty[slot]);
+        __syncwarp();
+        mbar_arrive_w(&s.tk_empty[slot]);
         if (!item_geometry(ticket, chain, i, n, n_low)) break;
         if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, DK_KI_FULL)) break;
         tc_fence_after_sync();
+        if (leader) LUCID_TR(args.trace, 2, trc, 35, n);
         if (n > 0) {
           if (!issue_s(g) || !issue_g(g, 0)) break;
         }
         for (int q = 0; q < n; ++q) {
           const uint32_t gq = g + q;
           if (q + 1 < n && !issue_s(gq + 1)) { alive = false; break; }
-          // W(q) written (and G read) by all 256 threads
+          // G(q) has been read (and W(q) written) by all 256 threads: the G buffer is free again
           if (!wait_barrier(&s.w_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_W_FULL)) { alive = false; break; }
           tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 2, trc, 34, gq);
           if (q + 1 < n && !issue_g(gq + 1, q + 1)) { alive = false; break; }
+        }
+        if (!alive) break;
+        g += n;
+        // K_i may be replaced once the S products of this item are complete
+        if (n > 0) umma_commit_w(&s.ki_free);
+        else mbar_arrive_w(&s.ki_free);
+      }
+    }
+  } else if (warp == 3) {
+    // =========================== W*K_j issuer ===========================
+    {
+      constexpr int fmt = kBf16 ? 1 : 0;
+      constexpr uint32_t idesc_wk = umma_idesc(fmt, 0, 1, 128, 128);   // ACC += W K_j: B rows = k
+      const uint64_t d_kr0_mn = umma_smem_desc(smem_u32(s.kring[0]), kHalfBytes, 1024);
+      uint32_t g = 0;
+      bool alive = true;
+      int trc = 0;
+      (void)trc;
+      const bool leader = (lane == 0);
+      (void)leader;
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, DK_TK_FULL)) break;
+        const int ticket = s.tk_slot[slot];
+        __syncwarp();
+        mbar_arrive_w(&s.tk_empty[slot]);
+        int chain, i, n, n_low;
+        if (!item_geometry(ticket, chain, i, n, n_low)) break;
+        for (int q = 0; q < n; ++q) {
+          const uint32_t gq = g + q;
+          // per-buffer barrier: the exp groups may be one tile ahead of this warp, never two on one buffer
+          if (!wait_barrier(&s.w_ready[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_W_READY)) {
+            alive = false;
+            break;
+          }
           if (q == 0 &&
               !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_ACC_FREE)) {
             alive = false;
             break;
           }
-          const int ks = gq % 3;
-          const uint32_t w_tmem = tmem + ((gq & 1) ? kDkS1 : kDkS0);
+          tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 5, trc, 50, gq);
+          const uint32_t ks = gq % 3;
+          const uint32_t buf = gq & 1;
+          const uint32_t w_tmem = tmem + (buf ? kDkS1 : kDkS0);
+          const uint64_t db = d_kr0_mn + ks * (kTileBytes >> 4);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             // W columns: k-steps 0-3 packed at columns 0-31, k-steps 4-7 at columns 64-95 of the S buffer
             const uint32_t a_col = (k < 4) ? k * 8 : 64 + (k - 4) * 8;
-            umma_ts(tmem + kDkAcc, w_tmem + a_col, desc_advance(d_kr_mn[ks], k * 2048), idesc_wk,
-                    (q | k) ? 1u : 0u);
+            umma_ts_w(tmem + kDkAcc, w_tmem + a_col, db + k * (2048 >> 4), idesc_wk, (q | k) ? 1u : 0u);
           }
-          umma_commit(&s.k_empty[ks]);
+          umma_commit_w(&s.k_empty[ks]);
+          umma_commit_w(&s.sbuf_free[buf]);
+          if (leader) LUCID_TR(args.trace, 5, trc, 51, gq);
         }
         if (!alive) break;
         g += n;
         // an item without tiles must not run ahead of the epilogue that still owns the previous phase
         if (n == 0 && !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_ACC_FREE)) break;
-        umma_commit(&s.acc_full);
-        umma_commit(&s.ki_free);
+        umma_commit_w(&s.acc_full);
       }
     }
   } else if (warp >= 4) {
@@ -267,6 +320,10 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     uint32_t g = 0;
     bool alive = true;
+    int trc = 0;
+    (void)trc;
+    const bool tr_lead = (tid == 128 || tid == 256);
+    (void)tr_lead;
     for (int it = 0; alive; ++it) {
       const int slot = it & 1;
       if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, DK_TK_FULL)) break;
@@ -278,41 +335,67 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
       const int b = chain / H, h = chain % H;
       for (int q = 0; q < n; ++q) {
         const uint32_t gq = g + q;
-        if (!wait_barrier(&s.s_full[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_S_FULL) ||
-            !wait_barrier(&s.g_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_G_FULL)) {
+        // Phase A needs only S: E = -exp(S) for this thread's 64 columns, kept in registers.  It
+        // overlaps the G product, which the tensor pipe can start only after the previous tile's G
+        // has been read.
+        if (!wait_barrier(&s.s_full[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_S_FULL)) {
           alive = false;
           break;
         }
         tc_fence_after_sync();
-        // diagonal tiles keep c <= r (D1, the last lower tile) or c >= r (D2, the first upper tile)
-        const int mask_mode = !diag_tiles ? 0 : (q == n_low - 1 ? 1 : (q == n_low ? 2 : 0));
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 40, gq);
         const uint32_t s_tmem = lane_base + ((gq & 1) ? kDkS1 : kDkS0) + wg * 64;
         const uint32_t g_tmem = lane_base + kDkG + wg * 64;
+        float ev[64];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t sv[32], gv[32];
+          uint32_t sv[32];
           tmem_ld32(s_tmem + c * 32, sv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ev[c * 32 + e] = -ex2_approx(__uint_as_float(sv[e]) * kLog2e);
+        }
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
+        // Diagonal tiles keep c <= r (D1, the last lower tile) or c >= r (D2, the first upper tile):
+        // the mask is applied to E here, once per tile, so that phase B stays branch-free.
+        const int mask_mode = !diag_tiles ? 0 : (q == n_low - 1 ? 1 : (q == n_low ? 2 : 0));
+        if (mask_mode) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            const int col = wg * 64 + e;
+            const bool keep = (mask_mode == 1) ? (col <= row) : (col >= row);
+            ev[e] = keep ? ev[e] : 0.f;
+          }
+        }
+        // Phase B: W = E o G, packed to 16 bits over the S columns.
+        if (!wait_barrier(&s.g_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_G_FULL)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 42, gq);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t gv[32];
           tmem_ld32(g_tmem + c * 32, gv);
           tmem_wait_ld();
+          if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 44 + 2 * c, gq);
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            float w0 = -ex2_approx(__uint_as_float(sv[2 * e]) * kLog2e) * __uint_as_float(gv[2 * e]);
-            float w1 = -ex2_approx(__uint_as_float(sv[2 * e + 1]) * kLog2e) * __uint_as_float(gv[2 * e + 1]);
-            if (mask_mode) {
-              const int col = wg * 64 + c * 32 + 2 * e;
-              const bool keep0 = (mask_mode == 1) ? (col <= row) : (col >= row);
-              const bool keep1 = (mask_mode == 1) ? (col + 1 <= row) : (col + 1 >= row);
-              w0 = keep0 ? w0 : 0.f;
-              w1 = keep1 ? w1 : 0.f;
-            }
+            const float w0 = ev[c * 32 + 2 * e] * __uint_as_float(gv[2 * e]);
+            const float w1 = ev[c * 32 + 2 * e + 1] * __uint_as_float(gv[2 * e + 1]);
             pk[e] = pack2<kBf16>(w0, w1);
           }
           tmem_st16(s_tmem + c * 16, pk);   // this group's W half sits at columns 64*wg .. 64*wg+31
+          if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 45 + 2 * c, gq);
         }
         tmem_wait_st();
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 48, gq);
         tc_fence_before_sync();
-        mbar_arrive(&s.w_full);
+        mbar_arrive(&s.w_full);             // to the S/G issuer: the G buffer has been read
+        mbar_arrive(&s.w_ready[gq & 1]);    // to the W*K_j issuer: W is in place
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 43, gq);
       }
       if (!alive) break;
       g += n;

@@ -11,6 +11,7 @@ struct SolveArgs {
   int* flags;             // (C, T)
   Control* ctl;
   long long* timestamps;  // (C, T, 8) or null
+  long long* trace;       // debugging builds only (LUCID_TRACE); null otherwise
   Problem p;
 };
 
@@ -26,6 +27,7 @@ struct DkArgs {
   void* dk;
   Strides dk_strides;
   Control* ctl;
+  long long* trace;       // debugging builds only (LUCID_TRACE); null otherwise
   Problem p;
 };
 

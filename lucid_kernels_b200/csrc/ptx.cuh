@@ -196,6 +196,25 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// Whole-warp variants: every lane of a converged warp calls them with warp-uniform arguments and one
+// elected lane issues the instruction.  Keeping the call sites convergent lets the compiler hold
+// descriptors and addresses in uniform registers.  elect.sync with a full mask names the same lane on
+// every call, so a commit tracks the MMAs issued through these wrappers.
+__device__ __forceinline__ void umma_ss_w(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if (elect_one()) umma_ss(d_tmem, adesc, bdesc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  if (elect_one()) umma_ts(d_tmem, a_tmem, bdesc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_commit_w(uint64_t* bar) {
+  if (elect_one()) umma_commit(bar);
+}
+__device__ __forceinline__ void mbar_arrive_w(uint64_t* bar) {
+  if (elect_one()) mbar_arrive(bar);
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMEM <-> registers.  Warp w of a 4-warp group owns lanes 32*(w%4) .. +31; each thread gets one row.
 // ---------------------------------------------------------------------------------------------

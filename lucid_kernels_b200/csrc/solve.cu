@@ -11,9 +11,11 @@
 // scaling exp(-|k_r|^2), stores Y_i and publishes flag[chain][i] with release semantics.  Consumers
 // acquire the flag before their TMA load of Y_i.
 //
-// Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 MMA issuer
-// and TMEM owner, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warps 4-7 / 8-11 two
-// exp groups that alternate over the S buffers and share the epilogue (64 columns each).
+// Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 issues the
+// S products and owns TMEM, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warp 3 issues the
+// P*Y and diagonal products, warps 4-7 / 8-11 two exp groups that alternate over the S buffers and share
+// the epilogue (64 columns each).  Two issuing warps because tcgen05.mma issue is nearly synchronous
+// with execution (the queue holds only a few instructions): the waits of one overlap the MMAs of the other.
 #include <type_traits>
 #include "kernels.h"
 
@@ -28,7 +30,7 @@ struct SolveSmem {
   alignas(8) uint64_t k_full[4];
   uint64_t k_empty[4], v_full[4], v_empty[4];
   uint64_t ki_full, ki_free, x_full, vi_full, xr_free;
-  uint64_t s_full[2], p_full[2];
+  uint64_t s_full[3], p_full[3], sbuf_free[3];
   uint64_t acc_full, acc_free, rhs_full, out_full, pub;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
@@ -39,11 +41,13 @@ struct SolveSmem {
 enum SolveBar : int {
   BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
   BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
-  BAR_TK_EMPTY, BAR_PUB
+  BAR_TK_EMPTY, BAR_PUB, BAR_SBUF_FREE
 };
 
 constexpr int kSolveThreads = 384;
-constexpr int kTmemS0 = 0, kTmemS1 = 128, kTmemAcc = 256, kTmemOut = 384;
+// Three S/P buffers (tile g uses buffer g % 3) and the accumulator; the diagonal product reuses the
+// accumulator's columns once the epilogue has read them.
+constexpr int kTmemS = 0, kTmemAcc = 384, kTmemOut = 384;
 
 template <bool kBf16, bool kReverse>
 __global__ void __launch_bounds__(kSolveThreads, 1)
@@ -73,11 +77,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     mbar_init(&s.x_full, 1);
     mbar_init(&s.vi_full, 1);
     mbar_init(&s.xr_free, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&s.s_full[i], 1);
       mbar_init(&s.p_full[i], 128);
+      mbar_init(&s.sbuf_free[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s.tk_full[i], 1);
-      mbar_init(&s.tk_empty[i], 10);
+      mbar_init(&s.tk_empty[i], 11);
     }
     mbar_init(&s.acc_full, 1);
     mbar_init(&s.acc_free, 256);
@@ -97,7 +104,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
   const uint32_t tmem = s.tmem_base;
 
   // Every role walks the same sequence of items; `it` counts items, `g` counts (i, j) tiles and `u`
-  // half-tiles, all per CTA, so that ring stages and barrier phases agree between roles.
+  // half-tiles, all per CTA, so that ring stages and barrier phases agree between roles.  Tile g uses
+  // S buffer g % 3 in phase (g / 3) & 1 and is exponentiated by group g & 1.
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& jfirst) -> bool {
     int step;
     if (!decode_ticket(ticket, P.C, T, P.group, chain, step)) return false;
@@ -121,6 +129,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       tma_prefetch_desc(&tm_x);
       uint32_t u = 0;
       bool alive = true;
+      int trc = 0;
+      (void)trc;
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_empty[slot], ((it >> 1) & 1) ^ 1, cta_abort, ctl, limit, -1, -1, BAR_TK_EMPTY)) break;
@@ -146,6 +156,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
             }
             mbar_expect_tx(&s.k_full[st], kHalfBytes);
             tma_load_4d(s.kring[st], &tm_k, &s.k_full[st], 64 * half, j * kBlock, h, b);
+            LUCID_TR(args.trace, 0, trc, 10, u);
           }
           if (alive && !x_loaded && mbar_try_wait(&s.xr_free, (it & 1) ^ 1)) {
             mbar_expect_tx(&s.x_full, kTileBytes);
@@ -169,6 +180,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       tma_prefetch_desc(&tm_out);
       uint32_t u = 0;
       bool alive = true;
+      int trc = 0;
+      (void)trc;
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, BAR_TK_FULL)) break;
@@ -198,6 +211,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
             }
             fence_proxy_async_all();   // flag acquired in the generic proxy; the tile is read by TMA
           }
+          LUCID_TR(args.trace, 1, trc, 20, q);
           for (int half = 0; half < 2; ++half, ++u) {
             const int st = u & 3;
             if (!wait_barrier(&s.v_empty[st], ((u >> 2) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_V_EMPTY)) {
@@ -207,6 +221,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
             mbar_expect_tx(&s.v_full[st], kHalfBytes);
             tma_load_4d(s.vring[st], &tm_out, &s.v_full[st], 0, j * kBlock + 64 * half, h, b);
             tma_load_4d(s.vring[st] + 8192, &tm_out, &s.v_full[st], 64, j * kBlock + 64 * half, h, b);
+            LUCID_TR(args.trace, 1, trc, 21, u);
           }
         }
         if (alive && !vi_loaded) {
@@ -217,105 +232,148 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       }
     }
   } else if (warp == 1) {
-    // =========================== MMA issuer (one lane) ===========================
-    if (lane == 0) {
+    // =========================== S issuer ===========================
+    // The whole warp walks the loop (uniform control flow, waits included); one elected lane issues.
+    {
+      const bool leader = (lane == 0);
+      (void)leader;
       constexpr int fmt = kBf16 ? 1 : 0;
       constexpr uint32_t idesc_s = umma_idesc(fmt, 0, 0, 128, 128);    // S = K_i K_j^T
-      constexpr uint32_t idesc_pv = umma_idesc(fmt, 0, 1, 128, 128);   // ACC += P Y_j   (B: rows = k)
-      constexpr uint32_t idesc_out = umma_idesc(fmt, kReverse ? 1 : 0, 1, 128, 128);  // OUT = X(^T) rhs
       const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
-      const uint64_t d_x = kReverse ? umma_smem_desc(smem_u32(s.x), kHalfBytes, 1024)
-                                    : umma_smem_desc(smem_u32(s.x), 16, 1024);
-      const uint64_t d_rhs = umma_smem_desc(smem_u32(s.rhs), kHalfBytes, 1024);
-      uint64_t d_kr[4], d_vr[4];
-      for (int i = 0; i < 4; ++i) {
-        d_kr[i] = umma_smem_desc(smem_u32(s.kring[i]), 16, 1024);
-        d_vr[i] = umma_smem_desc(smem_u32(s.vring[i]), 8192, 1024);
-      }
-      uint32_t g = 0;   // tiles issued so far (S buffer = g & 1)
+      const uint64_t d_kr0 = umma_smem_desc(smem_u32(s.kring[0]), 16, 1024);     // stage st: + st * 16 KiB
+      uint32_t g = 0;            // tiles issued so far
+      uint32_t buf = 0, ph = 0;  // g % 3 and (g / 3) & 1
       bool alive = true;
-      auto issue_s = [&](uint32_t gq) -> bool {
-        // S[gq & 1] = K_i K_j^T, two K panels of four k-steps each
-        const uint32_t dst = tmem + ((gq & 1) ? kTmemS1 : kTmemS0);
-        for (int half = 0; half < 2; ++half) {
-          const uint32_t u = gq * 2 + half;
-          const int st = u & 3;
-          if (!wait_barrier(&s.k_full[st], (u >> 2) & 1, cta_abort, ctl, limit, -1, -1, BAR_K_FULL)) return false;
-          tc_fence_after_sync();
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            umma_ss(dst, desc_advance(d_ki, half * kHalfBytes + kk * 32), desc_advance(d_kr[st], kk * 32), idesc_s,
-                    (half | kk) ? 1u : 0u);
-          }
-          umma_commit(&s.k_empty[st]);
-        }
-        umma_commit(&s.s_full[gq & 1]);
-        return true;
-      };
+      int trc = 0;
+      (void)trc;
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, BAR_TK_FULL)) break;
         const int ticket = s.tk_slot[slot];
-        mbar_arrive(&s.tk_empty[slot]);
+        __syncwarp();
+        mbar_arrive_w(&s.tk_empty[slot]);
         int chain, i, n, jfirst;
         if (!item_geometry(ticket, chain, i, n, jfirst)) break;
         if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_KI_FULL)) break;
         tc_fence_after_sync();
-        if (n > 0 && !issue_s(g)) break;
-        for (int q = 0; q < n; ++q) {
+        if (leader) LUCID_TR(args.trace, 2, trc, 35, n);
+        for (int q = 0; q < n; ++q, buf = (buf == 2 ? 0 : buf + 1), ph ^= (buf == 0)) {
           const uint32_t gq = g + q;
-          if (q + 1 < n) {
-            if (!issue_s(gq + 1)) { alive = false; break; }
-          } else {
-            umma_commit(&s.ki_free);   // every S product of this item has been issued
-          }
-          if (!wait_barrier(&s.p_full[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) {
+          // the P*Y product that read this buffer three tiles ago must have completed
+          if (!wait_barrier(&s.sbuf_free[buf], ph ^ 1, cta_abort, ctl, limit, chain, i, BAR_SBUF_FREE)) {
             alive = false;
             break;
           }
+          const uint32_t dst = tmem + kTmemS + buf * 128;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t u = gq * 2 + half;
+            const uint32_t st = u & 3;
+            if (!wait_barrier(&s.k_full[st], (u >> 2) & 1, cta_abort, ctl, limit, chain, i, BAR_K_FULL)) {
+              alive = false;
+              break;
+            }
+            tc_fence_after_sync();
+            if (leader) LUCID_TR(args.trace, 2, trc, 30, u);
+            const uint64_t da = desc_advance(d_ki, half * kHalfBytes);
+            const uint64_t db = d_kr0 + st * (kHalfBytes >> 4);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              umma_ss_w(dst, da + kk * 2, db + kk * 2, idesc_s, (half | kk) ? 1u : 0u);
+            }
+            umma_commit_w(&s.k_empty[st]);
+          }
+          if (!alive) break;
+          umma_commit_w(&s.s_full[buf]);
+          if (leader) LUCID_TR(args.trace, 2, trc, 31, gq);
+        }
+        if (!alive) break;
+        g += n;
+        // every S product of this item has been issued: K_i may be replaced once they complete
+        if (n > 0) umma_commit_w(&s.ki_free);
+        else mbar_arrive_w(&s.ki_free);
+      }
+    }
+  } else if (warp == 3) {
+    // =========================== P*Y and diagonal-product issuer ===========================
+    {
+      const bool leader = (lane == 0);
+      (void)leader;
+      constexpr int fmt = kBf16 ? 1 : 0;
+      constexpr uint32_t idesc_pv = umma_idesc(fmt, 0, 1, 128, 128);   // ACC += P Y_j   (B: rows = k)
+      constexpr uint32_t idesc_out = umma_idesc(fmt, kReverse ? 1 : 0, 1, 128, 128);  // OUT = X(^T) rhs
+      const uint64_t d_x = kReverse ? umma_smem_desc(smem_u32(s.x), kHalfBytes, 1024)
+                                    : umma_smem_desc(smem_u32(s.x), 16, 1024);
+      const uint64_t d_rhs = umma_smem_desc(smem_u32(s.rhs), kHalfBytes, 1024);
+      const uint64_t d_vr0 = umma_smem_desc(smem_u32(s.vring[0]), 8192, 1024);
+      uint32_t g = 0;
+      uint32_t buf = 0, ph = 0;  // g % 3 and (g / 3) & 1
+      bool alive = true;
+      int trc = 0;
+      (void)trc;
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, BAR_TK_FULL)) break;
+        const int ticket = s.tk_slot[slot];
+        __syncwarp();
+        mbar_arrive_w(&s.tk_empty[slot]);
+        int chain, i, n, jfirst;
+        if (!item_geometry(ticket, chain, i, n, jfirst)) break;
+        for (int q = 0; q < n; ++q, buf = (buf == 2 ? 0 : buf + 1), ph ^= (buf == 0)) {
+          const uint32_t gq = g + q;
+          if (!wait_barrier(&s.p_full[buf], ph, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) {
+            alive = false;
+            break;
+          }
+          if (leader) LUCID_TR(args.trace, 5, trc, 32, gq);
           if (q == 0 &&
               !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FREE)) {
             alive = false;
             break;
           }
-          const uint32_t p_tmem = tmem + ((gq & 1) ? kTmemS1 : kTmemS0);
-          for (int half = 0; half < 2 && alive; ++half) {
+          const uint32_t p_tmem = tmem + kTmemS + buf * 128;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
             const uint32_t u = gq * 2 + half;
-            const int st = u & 3;
+            const uint32_t st = u & 3;
             if (!wait_barrier(&s.v_full[st], (u >> 2) & 1, cta_abort, ctl, limit, chain, i, BAR_V_FULL)) {
               alive = false;
               break;
             }
             tc_fence_after_sync();
+            if (leader) LUCID_TR(args.trace, 5, trc, 33, u);
+            const uint64_t db = d_vr0 + st * (kHalfBytes >> 4);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              umma_ts(tmem + kTmemAcc, p_tmem + (half * 4 + kk) * 8, desc_advance(d_vr[st], kk * 2048), idesc_pv,
-                      (q | half | kk) ? 1u : 0u);
+              umma_ts_w(tmem + kTmemAcc, p_tmem + (half * 4 + kk) * 8, db + kk * (2048 >> 4), idesc_pv,
+                        (q | half | kk) ? 1u : 0u);
             }
-            umma_commit(&s.v_empty[st]);
+            umma_commit_w(&s.v_empty[st]);
           }
+          if (!alive) break;
+          umma_commit_w(&s.sbuf_free[buf]);
+          if (leader) LUCID_TR(args.trace, 5, trc, 34, gq);
         }
         if (!alive) break;
         g += n;
-        if (n == 0) {
-          mbar_arrive(&s.ki_free);   // nothing read K_i
-        }
-        umma_commit(&s.acc_full);
+        umma_commit_w(&s.acc_full);
         // diagonal step
         if (!wait_barrier(&s.rhs_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_RHS_FULL)) break;
         tc_fence_after_sync();
+        if (leader) LUCID_TR(args.trace, 5, trc, 36, 0);
         if (P.use_diag) {
           if (!wait_barrier(&s.x_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_X_FULL)) break;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint64_t da = kReverse ? desc_advance(d_x, k * 2048)
                                          : desc_advance(d_x, (k >> 2) * kHalfBytes + (k & 3) * 32);
-            umma_ss(tmem + kTmemOut, da, desc_advance(d_rhs, k * 2048), idesc_out, k ? 1u : 0u);
+            umma_ss_w(tmem + kTmemOut, da, desc_advance(d_rhs, k * 2048), idesc_out, k ? 1u : 0u);
           }
-          umma_commit(&s.out_full);
-          umma_commit(&s.xr_free);
+          umma_commit_w(&s.out_full);
+          umma_commit_w(&s.xr_free);
+          if (leader) LUCID_TR(args.trace, 5, trc, 37, 0);
         } else {
-          mbar_arrive(&s.xr_free);
+          mbar_arrive_w(&s.xr_free);
         }
       }
     }
@@ -324,9 +382,13 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     const int wg = (warp - 4) >> 2;                  // 0 or 1: S buffer parity, epilogue column panel
     const int row = ((warp & 3) << 5) + lane;        // TMEM lane == row of the block
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t s_tmem = lane_base + (wg ? kTmemS1 : kTmemS0);
     uint32_t g = 0;
+    uint32_t buf = 0, ph = 0;  // g % 3 and (g / 3) & 1
     bool alive = true;
+    int trc = 0;
+    (void)trc;
+    const bool tr_lead = (tid == 128 || tid == 256);
+    (void)tr_lead;
     for (int it = 0; alive; ++it) {
       const int slot = it & 1;
       if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, BAR_TK_FULL)) break;
@@ -341,14 +403,16 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       const float lam = P.use_diag ? args.lam_inv[(chain * T + i) * kBlock + row] : 1.0f;
 
       // ---- P = exp(S) for the tiles of my parity ----
-      for (int q = 0; q < n; ++q) {
+      for (int q = 0; q < n; ++q, buf = (buf == 2 ? 0 : buf + 1), ph ^= (buf == 0)) {
         const uint32_t gq = g + q;
         if ((gq & 1) != (uint32_t)wg) continue;
-        if (!wait_barrier(&s.s_full[wg], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
+        if (!wait_barrier(&s.s_full[buf], ph, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
           alive = false;
           break;
         }
         tc_fence_after_sync();
+        const uint32_t s_tmem = lane_base + kTmemS + buf * 128;
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 40, gq);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
@@ -365,7 +429,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&s.p_full[wg]);
+        mbar_arrive(&s.p_full[buf]);
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
       }
       if (!alive) break;
       g += n;
@@ -389,8 +454,13 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
 #pragma unroll
         for (int e = 0; e < 64; ++e) acc[e] = 0.f;
       }
-      tc_fence_before_sync();
-      mbar_arrive(&s.acc_free);
+      // The diagonal product is written over the accumulator, so with use_diag the accumulator is
+      // released only after that product has been read back (below).
+      if (!P.use_diag) {
+        tc_fence_before_sync();
+        mbar_arrive(&s.acc_free);
+      }
+      if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 42, n);
       long long t_loop = 0;
       if (P.instrument && tid == 128) t_loop = (long long)globaltimer_ns();
 
@@ -422,10 +492,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&s.rhs_full);
+      if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 43, 0);
 
       if (P.use_diag) {
         if (!wait_barrier(&s.out_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_OUT_FULL)) break;
         tc_fence_after_sync();
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 44, 0);
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           uint32_t v[32];
@@ -441,14 +513,20 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
             *reinterpret_cast<uint4*>(out_row + cc * 32 + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
+        tc_fence_before_sync();
+        mbar_arrive(&s.acc_free);
       }
-      // ---- publish: all 256 epilogue threads' stores, then one release store of the flag ----
-      __threadfence();
+      // ---- publish ----
+      // Each thread's stores are ordered before its (release) arrival on `pub`; the publishing thread
+      // acquires that barrier, then fences and releases the flag at GPU scope, so that an acquirer of
+      // the flag observes all 256 threads' stores.
       mbar_arrive(&s.pub);
       if (tid == 128) {
         if (!wait_barrier(&s.pub, it & 1, cta_abort, ctl, limit, chain, i, BAR_PUB)) break;
+        __threadfence();
         fence_proxy_async_all();
         st_release_gpu(args.flags + chain * T + i, 1);
+        LUCID_TR(args.trace, 3, trc, 45, i);
         if (P.instrument && args.timestamps) {
           long long* ts = args.timestamps + (long long)(chain * T + i) * 8;
           ts[0] = t_start;
