@@ -200,13 +200,18 @@ def main():
     # each rank materialises only its own systems, as a (1, N, n_local, 128) BSHD tensor
     K, V, dVp = orc.make_inputs(B, N, H, dtype=torch.bfloat16, hb_slice=(lo, hi))
     Kh, Vh, Gh = K.pin_memory(), V.pin_memory(), dVp.pin_memory()
-    Kd, Vd, Gd = Kh.to(dev), Vh.to(dev), Gh.to(dev)
+    # Two device copies of the inputs, used by alternate steps: every step then solves a k it has not seen in
+    # the previous call, so the forward always recomputes the diagonal-block inverses (only the backward
+    # of the same step reuses them, as it would in training).
+    sets = [(Kh.to(dev), Vh.to(dev), Gh.to(dev)) for _ in range(2)]
+    Kd, Vd, Gd = sets[0]
     f_fwd, f_rev, f_dk = flops_split(nsys, N)
     total_flops = f_fwd + f_rev + f_dk
 
-    def step():
-        vp = _forward_sub_fwd(Kd, Vd, use_diag_solve=True)
-        dv, dk = _forward_sub_bwd(Kd, vp, Gd, use_diag_solve=True, use_combined_kernel=True)
+    def step(i=0):
+        kd, vd, gd = sets[i & 1]
+        vp = _forward_sub_fwd(kd, vd, use_diag_solve=True)
+        dv, dk = _forward_sub_bwd(kd, vp, gd, use_diag_solve=True, use_combined_kernel=True)
         return vp, dv, dk
 
     def barrier():
@@ -214,8 +219,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
+    for w in range(args.warmup):
+        step(w)
     barrier()
 
     # ---- timed region: K steps, CUDA events on the launching stream, per-kernel events inside ----
@@ -235,10 +240,11 @@ def main():
     ev0.record()
     for s in range(args.steps):
         e = kern_ev[s]
+        kd, vd, gd = sets[(args.warmup + s) & 1]
         lib.lucid_profile_next_call(e[0].cuda_event, e[1].cuda_event, e[2].cuda_event, None)
-        vp = _forward_sub_fwd(Kd, Vd, use_diag_solve=True)
+        vp = _forward_sub_fwd(kd, vd, use_diag_solve=True)
         lib.lucid_profile_next_call(e[3].cuda_event, e[4].cuda_event, e[5].cuda_event, e[6].cuda_event)
-        dv, dk = _forward_sub_bwd(Kd, vp, Gd, use_diag_solve=True, use_combined_kernel=True)
+        dv, dk = _forward_sub_bwd(kd, vp, gd, use_diag_solve=True, use_combined_kernel=True)
     ev1.record()
     barrier()
     t_wall1 = time.time()
@@ -260,25 +266,59 @@ def main():
     # ---- e2e: host buffers in, host buffers out, through the operator interface ----
     e2e = None
     if not args.no_e2e:
+        # Every step copies its K, V, dV' from pinned host memory and copies V', dV, dK back to pinned host
+        # memory.  The copies run on their own streams and are double-buffered, so a step's uploads overlap
+        # the previous step's kernels and its downloads overlap the following kernels (V' leaves while the
+        # backward runs, dV while the dK kernel runs), the way a caller that feeds host data would drive it.
         outs_h = [torch.empty_like(Kh).pin_memory() for _ in range(3)]
-        def e2e_step():
-            kd = Kh.to(dev, non_blocking=True)
-            vd = Vh.to(dev, non_blocking=True)
-            gd = Gh.to(dev, non_blocking=True)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        main = torch.cuda.current_stream(dev)
+        dev_in = [[torch.empty_like(t, device=dev) for t in (Kh, Vh, Gh)] for _ in range(2)]
+        in_ready = [mk() for _ in range(2)]
+        in_free = [mk() for _ in range(2)]
+        for e in in_free:
+            e.record(main)
+
+        def e2e_step(i):
+            bi = i & 1
+            kd, vd, gd = dev_in[bi]
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(in_free[bi])          # the kernels of step i-2 are done with this buffer
+                kd.copy_(Kh, non_blocking=True)
+                vd.copy_(Vh, non_blocking=True)
+                gd.copy_(Gh, non_blocking=True)
+                in_ready[bi].record(s_in)
+            main.wait_event(in_ready[bi])
             vp = _forward_sub_fwd(kd, vd, use_diag_solve=True)
+            e_vp, e_dv, e_end = mk(), mk(), mk()
+            e_vp.record(main)
+            e_dv.record(main)                         # creates the handle; re-recorded after the reverse solve
+            lib.lucid_profile_next_call(None, None, e_dv.cuda_event, None)
             dv, dk = _forward_sub_bwd(kd, vp, gd, use_diag_solve=True, use_combined_kernel=True)
-            outs_h[0].copy_(vp, non_blocking=True)
-            outs_h[1].copy_(dv, non_blocking=True)
-            outs_h[2].copy_(dk, non_blocking=True)
-        for _ in range(2):
-            e2e_step()
+            e_end.record(main)
+            in_free[bi].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(e_vp)
+                outs_h[0].copy_(vp, non_blocking=True)
+                s_out.wait_event(e_dv)
+                outs_h[1].copy_(dv, non_blocking=True)
+                s_out.wait_event(e_end)
+                outs_h[2].copy_(dk, non_blocking=True)
+            for t in (vp, dv, dk):
+                t.record_stream(s_out)
+
+        for w in range(2):
+            e2e_step(w)
+        torch.cuda.synchronize()
         barrier()
-        n_e2e = max(3, min(args.steps, 10))
+        n_e2e = max(4, min(args.steps, 10))
         a, b_ = mk(), mk()
-        a.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        b_.record()
+        a.record(main)
+        for i in range(n_e2e):
+            e2e_step(i)
+        s_out.wait_stream(main)
+        b_.record(s_out)
+        torch.cuda.synchronize()
         barrier()
         te = torch.tensor([a.elapsed_time(b_)], device=dev, dtype=torch.float64)
         if world > 1:
@@ -310,7 +350,7 @@ def main():
                                 l2="inputs (3 x 128 MiB per step at N=32768) exceed the 126 MB L2; no flush",
                                 seed=0),
                     frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (world * peaks["bf16_tflops"]),
-                    roofline=roofline, clocks=clocks, gpu_launches=5 * args.steps, e2e=e2e)
+                    roofline=roofline, clocks=clocks, gpu_launches=4 * args.steps, e2e=e2e)
         if not args.no_cpu_baseline and world >= 1:
             cb, _ = cpu_naive_sample()
             line["cpu_baseline"] = cb

@@ -31,6 +31,10 @@ extern "C" {
 #define LUCID_FLAG_DIAG_SOLVE 1   /* apply inv(tril(exp(K_i K_i^T))) on the diagonal blocks           */
 #define LUCID_FLAG_NO_SYNC 2      /* skip inter-block flag waits (profiling only, results undefined)  */
 #define LUCID_FLAG_INSTRUMENT 4   /* record per-row-block timestamps in the workspace                  */
+#define LUCID_FLAG_REUSE_DIAG 8   /* the workspace still holds the diagonal-block inverses of THIS k from
+                                     the previous call (same values, same shape): skip recomputing them.
+                                     The reference recomputes them in every call
+                                     (forward_sub_interface.py:116,230,311).                            */
 
 /* backward modes */
 #define LUCID_BWD_DV_ONLY 0       /* dV only                                                          */
@@ -83,6 +87,13 @@ const char* lucid_status_string(int code);
 /* Sets the time limit (nanoseconds) of every device-side wait; default 2e9. */
 void lucid_set_wait_limit_ns(uint64_t ns);
 
+/* Scheduler knob: how many of a chain group's first (short, latency-bound) row-blocks are interleaved with
+ * the last row-blocks of the previous group (at most T/2); negative restores the default (0: measured
+ * slower on B200 whenever enabled, kept as an experiment knob).  No
+ * counterpart in the reference, whose grid is one CTA per row-block in launch order
+ * (tile_scheduler.py:105-117). */
+void lucid_set_group_overlap(int steps);
+
 /* Per-kernel timing for benchmarks: the NEXT lucid_fwd_sub / lucid_bwd_sub call records these
  * cudaEvent_t handles on its stream (before the diagonal-prep kernel, after it, after the solve kernel,
  * after the dK kernel); any of them may be NULL.  The handles are forgotten after that call.  Stands in
@@ -90,7 +101,7 @@ void lucid_set_wait_limit_ns(uint64_t ns);
 void lucid_profile_next_call(void* ev_begin, void* ev_after_prep, void* ev_after_solve, void* ev_after_dk);
 
 /* Offsets inside the workspace, for tools that read the instrumentation:
- * timestamps are int64[(B*H)][T][8] = {start, loop end, published, ns spent in flag waits, CTA, tiles}
+ * timestamps are int64[(B*H)][T][8] = {start, loop end, published, ns spent in flag waits, CTA, tiles, SM cycles start..published}
  * (cf. the (T, 8) buffer of forward_sub_interface.py:103). */
 size_t lucid_workspace_timestamps_offset(int B, int N, int H);
 

@@ -8,6 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
+import weakref
 from typing import Dict, Tuple
 
 import torch
@@ -19,6 +20,7 @@ _lock = threading.Lock()
 FLAG_DIAG_SOLVE = 1
 FLAG_NO_SYNC = 2
 FLAG_INSTRUMENT = 4
+FLAG_REUSE_DIAG = 8
 BWD_DV_ONLY = 0
 BWD_COMBINED = 1
 
@@ -26,7 +28,7 @@ _I64x3 = ctypes.c_int64 * 3
 
 EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_read_status",
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
-           "lucid_profile_next_call")
+           "lucid_profile_next_call", "lucid_set_group_overlap")
 
 
 class LucidKernelError(RuntimeError):
@@ -68,6 +70,8 @@ def load() -> ctypes.CDLL:
         lib.lucid_read_status.argtypes = [c.c_void_p, c.c_void_p, c.POINTER(c.c_int32)]
         lib.lucid_status_string.restype = c.c_char_p
         lib.lucid_status_string.argtypes = [c.c_int]
+        lib.lucid_set_group_overlap.restype = None
+        lib.lucid_set_group_overlap.argtypes = [c.c_int]
         lib.lucid_profile_next_call.restype = None
         lib.lucid_profile_next_call.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
         lib.lucid_set_wait_limit_ns.restype = None
@@ -107,6 +111,29 @@ def workspace(device: torch.device, stream_ptr: int, B: int, N: int, H: int) -> 
             _workspaces.clear()
         _workspaces[key] = ws
     return ws
+
+
+# What each workspace last prepared its diagonal-block inverses for.  They depend on k only, so a
+# backward call that follows the forward call on the same k can skip recomputing them.  "Same k" means
+# the same live tensor object with an unchanged version counter: the address alone is not enough,
+# because the caching allocator hands a freed block to the next tensor of that size.
+_diag_keys: Dict[int, tuple] = {}
+
+
+def _diag_key(k: torch.Tensor) -> tuple:
+    return (k.data_ptr(), k._version, tuple(k.shape), tuple(k.stride()), k.dtype)
+
+
+def diag_is_cached(ws: torch.Tensor, k: torch.Tensor) -> bool:
+    entry = _diag_keys.get(ws.data_ptr())
+    return entry is not None and entry[0]() is k and entry[1] == _diag_key(k)
+
+
+def diag_remember(ws: torch.Tensor, k: torch.Tensor, valid: bool) -> None:
+    if valid:
+        _diag_keys[ws.data_ptr()] = (weakref.ref(k), _diag_key(k))
+    else:
+        _diag_keys.pop(ws.data_ptr(), None)
 
 
 def check_rc(rc: int, what: str) -> None:

@@ -26,31 +26,6 @@ struct PrepSmem {
   int abort_flag;
 };
 
-// One elimination step of the column sweep, with the row index a compile-time constant so that the
-// running column y[] stays in registers: y[r] -= N[r][k] * y[k] for r > k.
-template <int K>
-__device__ __forceinline__ void sweep_step(float (&y)[kBlock], const float (*nt)[kBlock]) {
-  const float xk = y[K];
-  constexpr int r0 = (K + 4) & ~3;   // first multiple of four above K
-#pragma unroll
-  for (int r = K + 1; r < r0; ++r) y[r] = fmaf(-nt[K][r], xk, y[r]);
-#pragma unroll
-  for (int r = r0; r < kBlock; r += 4) {
-    const float4 n4 = *reinterpret_cast<const float4*>(&nt[K][r]);
-    y[r] = fmaf(-n4.x, xk, y[r]);
-    y[r + 1] = fmaf(-n4.y, xk, y[r + 1]);
-    y[r + 2] = fmaf(-n4.z, xk, y[r + 2]);
-    y[r + 3] = fmaf(-n4.w, xk, y[r + 3]);
-  }
-}
-template <int K>
-__device__ __forceinline__ void sweep_from(float (&y)[kBlock], const float (*nt)[kBlock], int kmin) {
-  if constexpr (K < kBlock - 1) {
-    if (K >= kmin) sweep_step<K>(y, nt);
-    sweep_from<K + 1>(y, nt, kmin);
-  }
-}
-
 template <bool kBf16>
 __global__ void __launch_bounds__(128) diag_prep_kernel(const __grid_constant__ CUtensorMap tm_k, const PrepArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -119,18 +94,49 @@ __global__ void __launch_bounds__(128) diag_prep_kernel(const __grid_constant__ 
   __syncthreads();
 
   // ---- column sweep: thread c owns column c of X = (I + N)^-1 ----
+  // Rows are taken in panels of 16.  Panel p first subtracts the contribution of the rows already
+  // solved (a rolled loop over k with the 16 running values in registers), then solves its own 16 x 16
+  // unit-triangular block.  Solved values X[k][c] (k >= c) are parked in nt[k][c], the half of `nt`
+  // that N does not use, where thread c reads them back conflict-free.
   if (ok) {
-    float y[kBlock];
-#pragma unroll
-    for (int r = 0; r < kBlock; ++r) y[r] = (r == tid) ? 1.f : 0.f;
-    sweep_from<0>(y, s.nt, warp * 32);   // columns of warp w are zero above row 32*w
-    // stage X[r][tid] as 16-bit row-major in the (now idle) K buffer
     typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
-    elem_t* stage = reinterpret_cast<elem_t*>(s.k);
+    elem_t* stage = reinterpret_cast<elem_t*>(s.k);   // X as 16-bit row-major, in the (now idle) K buffer
+    const int c = tid;
+    const int kstart = warp * 32;                     // rows above 32*warp are zero for the whole warp
+#pragma unroll 1
+    for (int p = 0; p < kBlock / 16; ++p) {
+      const int r0 = p * 16;
+      float y[16];
 #pragma unroll
-    for (int r = 0; r < kBlock; ++r) {
-      if constexpr (kBf16) stage[r * kBlock + tid] = __float2bfloat16_rn(y[r]);
-      else stage[r * kBlock + tid] = __float2half_rn(y[r]);
+      for (int j = 0; j < 16; ++j) y[j] = (r0 + j == c) ? 1.f : 0.f;
+      if (r0 + 15 >= kstart) {
+#pragma unroll 4
+        for (int k = kstart; k < r0; ++k) {
+          const float xk = (k >= c) ? s.nt[k][c] : 0.f;
+          const float4* nrow = reinterpret_cast<const float4*>(&s.nt[k][r0]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 n4 = nrow[q];
+            y[4 * q + 0] = fmaf(-n4.x, xk, y[4 * q + 0]);
+            y[4 * q + 1] = fmaf(-n4.y, xk, y[4 * q + 1]);
+            y[4 * q + 2] = fmaf(-n4.z, xk, y[4 * q + 2]);
+            y[4 * q + 3] = fmaf(-n4.w, xk, y[4 * q + 3]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float xj = y[j];
+#pragma unroll
+          for (int jj = j + 1; jj < 16; ++jj) y[jj] = fmaf(-s.nt[r0 + j][r0 + jj], xj, y[jj]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int r = r0 + j;
+        if (r >= c) s.nt[r][c] = y[j];
+        if constexpr (kBf16) stage[r * kBlock + c] = __float2bfloat16_rn(r >= c ? y[j] : 0.f);
+        else stage[r * kBlock + c] = __float2half_rn(r >= c ? y[j] : 0.f);
+      }
     }
   }
   __syncthreads();

@@ -258,6 +258,33 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA and ALU pipes, for use beside ex2.approx when the MUFU pipe (16 results per clock per
+// SM) is the bottleneck.  Cody-Waite split: adding 1.5 * 2^23 rounds x to the nearest integer n in the
+// low mantissa bits; 2^f for f = x - n in [-0.5, 0.5] is a degree-3 minimax polynomial (max relative
+// error 7.5e-5, twenty times below a bf16 half-ulp); n is added into the exponent field.  Inputs are
+// clamped to [-125, 125] so the exponent arithmetic cannot wrap.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fminf(fmaxf(x, -125.f), 125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0551716610789299f, 0.2426111251115799f);
+  p = fmaf(p, f, 0.6932609677314758f);
+  p = fmaf(p, f, 0.9999280571937561f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// Element e of a row uses the polynomial when e % kExpPolyPeriod == kExpPolyPeriod - 1 (0 disables it).
+// Measured on B200 (B=2, N=32768, H=8): periods 2, 3 and 4 were all slower than 0, because a polynomial
+// costs about as many FMA + ALU issue cycles per warp as the 8 cycles of one MUFU instruction, so it
+// is off by default.
+#ifndef LUCID_EXP_POLY_PERIOD
+#define LUCID_EXP_POLY_PERIOD 0
+#endif
+constexpr int kExpPolyPeriod = LUCID_EXP_POLY_PERIOD;
+__device__ __forceinline__ float ex2_mixed(float x, int e) {
+  if (kExpPolyPeriod > 0 && (e % (kExpPolyPeriod > 0 ? kExpPolyPeriod : 1)) == kExpPolyPeriod - 1) return ex2_poly(x);
+  return ex2_approx(x);
+}
+
 // pack two fp32 into one 32-bit word of bf16 (is_bf16) or fp16, round-to-nearest-even; `lo` lands in
 // the low half (the lower K / column index).
 template <bool kBf16>

@@ -30,7 +30,7 @@ struct SolveSmem {
   alignas(8) uint64_t k_full[4];
   uint64_t k_empty[4], v_full[4], v_empty[4];
   uint64_t ki_full, ki_free, x_full, vi_full, xr_free;
-  uint64_t s_full[3], p_full[3], sbuf_free[3];
+  uint64_t s_full[2], s_free[2], p_full[2], p_free[2];
   uint64_t acc_full, acc_free, rhs_full, out_full, pub;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
@@ -41,13 +41,17 @@ struct SolveSmem {
 enum SolveBar : int {
   BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
   BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
-  BAR_TK_EMPTY, BAR_PUB, BAR_SBUF_FREE
+  BAR_TK_EMPTY, BAR_PUB, BAR_S_FREE, BAR_P_FREE
 };
 
 constexpr int kSolveThreads = 384;
-// Three S/P buffers (tile g uses buffer g % 3) and the accumulator; the diagonal product reuses the
-// accumulator's columns once the epilogue has read them.
-constexpr int kTmemS = 0, kTmemAcc = 384, kTmemOut = 384;
+// TMEM columns: two S buffers (fp32, 128 columns each), two P buffers (16-bit pairs, 64 columns each)
+// and the accumulator; the diagonal product reuses the accumulator's columns once the epilogue has
+// read them.  Tile g uses S[g & 1] and P[g & 1].
+constexpr int kTmemS = 0, kTmemP = 256, kTmemAcc = 384, kTmemOut = 384;
+// Register budget per thread after the role split: the exp / epilogue groups hold a whole S row (128
+// fp32) in registers, the four service warps need few.  128 * 56 + 256 * 224 = 64512 <= 65536.
+constexpr int kRegsService = 72, kRegsExp = 216;
 
 template <bool kBf16, bool kReverse>
 __global__ void __launch_bounds__(kSolveThreads, 1)
@@ -77,12 +81,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     mbar_init(&s.x_full, 1);
     mbar_init(&s.vi_full, 1);
     mbar_init(&s.xr_free, 1);
-    for (int i = 0; i < 3; ++i) {
-      mbar_init(&s.s_full[i], 1);
-      mbar_init(&s.p_full[i], 128);
-      mbar_init(&s.sbuf_free[i], 1);
-    }
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.s_free[i], 128);
+      mbar_init(&s.p_full[i], 128);
+      mbar_init(&s.p_free[i], 1);
       mbar_init(&s.tk_full[i], 1);
       mbar_init(&s.tk_empty[i], 11);
     }
@@ -105,10 +108,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
 
   // Every role walks the same sequence of items; `it` counts items, `g` counts (i, j) tiles and `u`
   // half-tiles, all per CTA, so that ring stages and barrier phases agree between roles.  Tile g uses
-  // S buffer g % 3 in phase (g / 3) & 1 and is exponentiated by group g & 1.
+  // buffers g & 1 in phase (g >> 1) & 1 and is exponentiated by group g & 1.
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& jfirst) -> bool {
     int step;
-    if (!decode_ticket(ticket, P.C, T, P.group, chain, step)) return false;
+    if (!decode_ticket(ticket, P.C, T, P.group, P.overlap, chain, step)) return false;
     if (kReverse) {
       i = T - 1 - step;
       n = step;           // blocks i+1 .. T-1, visited from T-1 down to i+1
@@ -122,7 +125,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
   };
   auto tile_j = [&](int jfirst, int q) -> int { return kReverse ? jfirst - q : jfirst + q; };
 
+  // Each role sets its register budget inside its own branch, so that the compiler ties the budget to
+  // the code that runs under it (warps 0-3 form one warpgroup and all execute the same decrease).
   if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
     // =========================== K producer (one lane) ===========================
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
@@ -174,6 +180,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       }
     }
   } else if (warp == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
     // =========================== Y producer (one lane) ===========================
     if (lane == 0) {
       tma_prefetch_desc(&tm_in);
@@ -232,6 +239,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       }
     }
   } else if (warp == 1) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
     // =========================== S issuer ===========================
     // The whole warp walks the loop (uniform control flow, waits included); one elected lane issues.
     {
@@ -242,7 +250,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
       const uint64_t d_kr0 = umma_smem_desc(smem_u32(s.kring[0]), 16, 1024);     // stage st: + st * 16 KiB
       uint32_t g = 0;            // tiles issued so far
-      uint32_t buf = 0, ph = 0;  // g % 3 and (g / 3) & 1
       bool alive = true;
       int trc = 0;
       (void)trc;
@@ -257,13 +264,15 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_KI_FULL)) break;
         tc_fence_after_sync();
         if (leader) LUCID_TR(args.trace, 2, trc, 35, n);
-        for (int q = 0; q < n; ++q, buf = (buf == 2 ? 0 : buf + 1), ph ^= (buf == 0)) {
+        for (int q = 0; q < n; ++q) {
           const uint32_t gq = g + q;
-          // the P*Y product that read this buffer three tiles ago must have completed
-          if (!wait_barrier(&s.sbuf_free[buf], ph ^ 1, cta_abort, ctl, limit, chain, i, BAR_SBUF_FREE)) {
+          const uint32_t buf = gq & 1;
+          // the exp group has copied this buffer's previous tile (two tiles ago) into registers
+          if (!wait_barrier(&s.s_free[buf], ((gq >> 1) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_S_FREE)) {
             alive = false;
             break;
           }
+          tc_fence_after_sync();
           const uint32_t dst = tmem + kTmemS + buf * 128;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
@@ -295,6 +304,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       }
     }
   } else if (warp == 3) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
     // =========================== P*Y and diagonal-product issuer ===========================
     {
       const bool leader = (lane == 0);
@@ -307,7 +317,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       const uint64_t d_rhs = umma_smem_desc(smem_u32(s.rhs), kHalfBytes, 1024);
       const uint64_t d_vr0 = umma_smem_desc(smem_u32(s.vring[0]), 8192, 1024);
       uint32_t g = 0;
-      uint32_t buf = 0, ph = 0;  // g % 3 and (g / 3) & 1
       bool alive = true;
       int trc = 0;
       (void)trc;
@@ -319,9 +328,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         mbar_arrive_w(&s.tk_empty[slot]);
         int chain, i, n, jfirst;
         if (!item_geometry(ticket, chain, i, n, jfirst)) break;
-        for (int q = 0; q < n; ++q, buf = (buf == 2 ? 0 : buf + 1), ph ^= (buf == 0)) {
+        for (int q = 0; q < n; ++q) {
           const uint32_t gq = g + q;
-          if (!wait_barrier(&s.p_full[buf], ph, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) {
+          const uint32_t buf = gq & 1;
+          if (!wait_barrier(&s.p_full[buf], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) {
             alive = false;
             break;
           }
@@ -331,7 +341,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
             alive = false;
             break;
           }
-          const uint32_t p_tmem = tmem + kTmemS + buf * 128;
+          const uint32_t p_tmem = tmem + kTmemP + buf * 64;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             const uint32_t u = gq * 2 + half;
@@ -351,7 +361,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
             umma_commit_w(&s.v_empty[st]);
           }
           if (!alive) break;
-          umma_commit_w(&s.sbuf_free[buf]);
+          umma_commit_w(&s.p_free[buf]);
           if (leader) LUCID_TR(args.trace, 5, trc, 34, gq);
         }
         if (!alive) break;
@@ -378,12 +388,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       }
     }
   } else if (warp >= 4) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsExp));
     // =========================== exp groups + epilogue ===========================
     const int wg = (warp - 4) >> 2;                  // 0 or 1: S buffer parity, epilogue column panel
     const int row = ((warp & 3) << 5) + lane;        // TMEM lane == row of the block
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     uint32_t g = 0;
-    uint32_t buf = 0, ph = 0;  // g % 3 and (g / 3) & 1
     bool alive = true;
     int trc = 0;
     (void)trc;
@@ -398,38 +408,58 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       int chain, i, n, jfirst;
       if (!item_geometry(ticket, chain, i, n, jfirst)) break;
       const int b = chain / H, h = chain % H;
-      long long t_start = 0;
-      if (P.instrument && tid == 128) t_start = (long long)globaltimer_ns();
+      long long t_start = 0, c_start = 0;
+      if (P.instrument && tid == 128) {
+        t_start = (long long)globaltimer_ns();
+        c_start = clock64();
+      }
       const float lam = P.use_diag ? args.lam_inv[(chain * T + i) * kBlock + row] : 1.0f;
 
       // ---- P = exp(S) for the tiles of my parity ----
-      for (int q = 0; q < n; ++q, buf = (buf == 2 ? 0 : buf + 1), ph ^= (buf == 0)) {
+      for (int q = 0; q < n; ++q) {
         const uint32_t gq = g + q;
         if ((gq & 1) != (uint32_t)wg) continue;
-        if (!wait_barrier(&s.s_full[buf], ph, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
+        const uint32_t ph = (gq >> 1) & 1;
+        if (!wait_barrier(&s.s_full[wg], ph, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
           alive = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t s_tmem = lane_base + kTmemS + buf * 128;
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 40, gq);
+        // the whole S row goes to registers at once, which frees the S buffer for the tile after next
+        uint32_t v[128];
+        {
+          const uint32_t s_tmem = lane_base + kTmemS + wg * 128;
+          tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+          tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+          tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
+          tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
+          tmem_wait_ld();
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&s.s_free[wg]);
+        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 46, gq);
+        // P[wg] was read by the P*Y product of two tiles ago
+        if (!wait_barrier(&s.p_free[wg], ph ^ 1, cta_abort, ctl, limit, chain, i, BAR_P_FREE)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t p_tmem = lane_base + kTmemP + wg * 64;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(s_tmem + c * 32, v);
-          tmem_wait_ld();
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            const float e0 = ex2_approx(__uint_as_float(v[2 * e]) * kLog2e);
-            const float e1 = ex2_approx(__uint_as_float(v[2 * e + 1]) * kLog2e);
+            const float e0 = ex2_mixed(__uint_as_float(v[c * 32 + 2 * e]) * kLog2e, c * 32 + 2 * e);
+            const float e1 = ex2_mixed(__uint_as_float(v[c * 32 + 2 * e + 1]) * kLog2e, c * 32 + 2 * e + 1);
             pk[e] = pack2<kBf16>(e0, e1);
           }
-          tmem_st16(s_tmem + c * 16, pk);   // P overwrites the S columns already consumed
+          tmem_st16(p_tmem + c * 16, pk);
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&s.p_full[buf]);
+        mbar_arrive(&s.p_full[wg]);
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
       }
       if (!alive) break;
@@ -518,13 +548,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       }
       // ---- publish ----
       // Each thread's stores are ordered before its (release) arrival on `pub`; the publishing thread
-      // acquires that barrier, then fences and releases the flag at GPU scope, so that an acquirer of
-      // the flag observes all 256 threads' stores.
+      // acquires that barrier and then releases the flag at GPU scope, so that an acquirer of the flag
+      // observes all 256 threads' stores (the consumer orders its TMA read after the acquire with a
+      // proxy fence).
       mbar_arrive(&s.pub);
       if (tid == 128) {
         if (!wait_barrier(&s.pub, it & 1, cta_abort, ctl, limit, chain, i, BAR_PUB)) break;
-        __threadfence();
-        fence_proxy_async_all();
         st_release_gpu(args.flags + chain * T + i, 1);
         LUCID_TR(args.trace, 3, trc, 45, i);
         if (P.instrument && args.timestamps) {
@@ -534,6 +563,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
           ts[2] = (long long)globaltimer_ns();
           ts[4] = blockIdx.x;
           ts[5] = n;
+          ts[6] = clock64() - c_start;   // SM cycles from start to publication (ts[2] - ts[0] in ns)
         }
       }
     }

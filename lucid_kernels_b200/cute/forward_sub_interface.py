@@ -14,6 +14,9 @@ is a drop-in for ``from lucid_kernels.cute import ...``.  Differences, all behin
 * ``_forward_sub_bwd_combined`` returns the FULL dK (off-diagonal and diagonal terms);
 * ``use_combined_kernel=False`` still returns the full dK: the dense host formula the reference uses
   there (``_backward_dk_reference``, O(T^2) fp32 temporaries) is an oracle, not a product path;
+* a call whose k is the tensor of the previous call on the same stream (same storage, unchanged
+  version counter), such as the backward after the forward, reuses the diagonal-block inverses
+  still in the workspace (``LUCID_B200_REUSE_DIAG=0`` turns this off);
 * inter-block waits are bounded: with ``check=True`` (or ``LUCID_B200_CHECK=1``) the call
   synchronises and raises if a wait ran out instead of hanging.
 
@@ -33,6 +36,10 @@ __all__ = ["_forward_sub_fwd", "_forward_sub_bwd", "_forward_sub_bwd_dv", "_forw
 
 _CHECK_DEFAULT = os.environ.get("LUCID_B200_CHECK", "0") not in ("0", "", "false")
 _GROUP_DEFAULT = int(os.environ.get("LUCID_B200_CHAIN_GROUP", "0"))
+# Reuse the diagonal-block inverses left in the workspace by the previous call when k is unchanged (same
+# storage and version counter), e.g. the backward call that follows a forward call.  LUCID_B200_REUSE_DIAG=0
+# recomputes them in every call, as the reference does.
+_REUSE_DIAG = os.environ.get("LUCID_B200_REUSE_DIAG", "1") not in ("0", "", "false")
 
 
 def maybe_contiguous(x):
@@ -82,10 +89,11 @@ def _forward_sub_fwd(
 
     Returns ``v_prime`` (same shape and dtype as ``v``), or ``(v_prime, timestamps)`` with
     ``instrument``; timestamps are int64 ``(batch*heads, T, 8)`` =
-    {start ns, loop end ns, published ns, ns spent waiting on flags, CTA, tiles, 0, 0}.
+    {start ns, loop end ns, published ns, ns spent waiting on flags, CTA, tiles, SM cycles, 0}.
     """
     k, v = [maybe_contiguous(t) for t in (k, v)]
     B, N, H, D = _common_asserts(k, (v,), block_size)
+    k_in = k
     k, v = _aligned(k.detach()), _aligned(v.detach())
     lib = _cabi.load()
     v_prime = torch.empty_like(v, memory_format=torch.contiguous_format)
@@ -94,12 +102,16 @@ def _forward_sub_fwd(
         ws = _cabi.workspace(k.device, stream, B, N, H)
         flags = ((_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_NO_SYNC if no_sync else 0) |
                  (_cabi.FLAG_INSTRUMENT if instrument else 0))
+        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in):
+            flags |= _cabi.FLAG_REUSE_DIAG
         rc = lib.lucid_fwd_sub(k.data_ptr(), v.data_ptr(), v_prime.data_ptr(), _cabi.strides3(k),
                                _cabi.strides3(v), _cabi.strides3(v_prime), B, N, H, D, _cabi.dtype_code(k.dtype),
                                flags, 0 if window_size is None else int(window_size),
                                _GROUP_DEFAULT if chain_group is None else int(chain_group),
                                ws.data_ptr(), ws.numel(), stream)
         _cabi.check_rc(rc, "lucid_fwd_sub")
+        # the inverses now in the workspace belong to k_in, provided the kernels read k_in's own storage
+        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr())
         if _CHECK_DEFAULT if check is None else check:
             _cabi.raise_on_device_error(ws, stream, "_forward_sub_fwd")
     if instrument:
@@ -107,8 +119,9 @@ def _forward_sub_fwd(
     return v_prime
 
 
-def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, chain_group, what):
+def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, chain_group, what, k_in=None):
     B, N, H, D = k.shape
+    k_in = k if k_in is None else k_in
     lib = _cabi.load()
     dv = torch.empty_like(dv_prime, memory_format=torch.contiguous_format)
     dk = torch.empty_like(k, memory_format=torch.contiguous_format) if mode == _cabi.BWD_COMBINED else None
@@ -116,6 +129,8 @@ def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, cha
     with torch.cuda.device(k.device):
         ws = _cabi.workspace(k.device, stream, B, N, H)
         flags = (_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_INSTRUMENT if instrument else 0)
+        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in):
+            flags |= _cabi.FLAG_REUSE_DIAG
         vp_ptr = v_prime.data_ptr() if v_prime is not None else None
         vp_str = _cabi.strides3(v_prime) if v_prime is not None else _cabi.strides3(k)
         rc = lib.lucid_bwd_sub(k.data_ptr(), vp_ptr, dv_prime.data_ptr(), dv.data_ptr(),
@@ -126,6 +141,7 @@ def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, cha
                                _GROUP_DEFAULT if chain_group is None else int(chain_group),
                                ws.data_ptr(), ws.numel(), stream)
         _cabi.check_rc(rc, what)
+        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr())
         if _CHECK_DEFAULT if check is None else check:
             _cabi.raise_on_device_error(ws, stream, what)
     ts = _timestamps_view(ws, B, N, H).clone() if instrument else None
@@ -146,9 +162,10 @@ def _forward_sub_bwd_dv(
     block to the first."""
     k, dv_prime = [maybe_contiguous(t) for t in (k, dv_prime)]
     _common_asserts(k, (dv_prime,), block_size)
+    k_in = k
     k, dv_prime = _aligned(k.detach()), _aligned(dv_prime.detach())
     dv, _, ts = _bwd_call(k, None, dv_prime, _cabi.BWD_DV_ONLY, use_diag_solve, instrument, check, chain_group,
-                          "_forward_sub_bwd_dv")
+                          "_forward_sub_bwd_dv", k_in=k_in)
     if instrument:
         return dv, ts
     return dv
@@ -168,9 +185,10 @@ def _forward_sub_bwd_combined(
     """(dv, dk).  Unlike the reference, ``dk`` already contains the diagonal-block term."""
     k, v_prime, dv_prime = [maybe_contiguous(t) for t in (k, v_prime, dv_prime)]
     _common_asserts(k, (v_prime, dv_prime), block_size)
+    k_in = k
     k, v_prime, dv_prime = [_aligned(t.detach()) for t in (k, v_prime, dv_prime)]
     dv, dk, ts = _bwd_call(k, v_prime, dv_prime, _cabi.BWD_COMBINED, use_diag_solve, instrument, check,
-                           chain_group, "_forward_sub_bwd_combined")
+                           chain_group, "_forward_sub_bwd_combined", k_in=k_in)
     if instrument:
         return dv, dk, ts
     return dv, dk

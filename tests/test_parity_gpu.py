@@ -179,3 +179,32 @@ def test_argument_errors(ops):
         ops._forward_sub_fwd(K.cuda(), V.cuda().half())                     # mixed dtypes
     with pytest.raises(AssertionError):
         ops._forward_sub_fwd(K, V)                                          # not on CUDA
+
+
+def test_diag_inverse_reuse_is_safe(ops):
+    """The backward after a forward on the same k object reuses the diagonal-block inverses left in the
+    workspace; a different k (even one that lands at the same address) or an in-place update must not."""
+    from lucid_kernels_b200 import _cabi
+
+    K, V, G = orc.make_inputs(1, 512, 2, dtype=torch.bfloat16, seed=5)
+    Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+    vp = ops._forward_sub_fwd(Kc, Vc, check=True)
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = _cabi.workspace(Kc.device, stream, 1, 512, 2)
+    assert _cabi.diag_is_cached(ws, Kc)
+    dv_cached, dk_cached = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+    _cabi.diag_remember(ws, Kc, False)                     # force recomputation
+    dv_fresh, dk_fresh = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+    assert torch.equal(dv_cached, dv_fresh) and torch.equal(dk_cached, dk_fresh)
+    # a new tensor of the same shape, possibly at the same address, is not a cache hit
+    addr = Kc.data_ptr()
+    del Kc
+    K2, V2, _ = orc.make_inputs(1, 512, 2, dtype=torch.bfloat16, seed=6)
+    K2c = K2.cuda()
+    vp2 = ops._forward_sub_fwd(K2c, V2.cuda(), check=True)
+    assert orc.rel_err(vp2, orc.forward_sub_blockwise(K2, V2)) < 0.01, (addr == K2c.data_ptr())
+    # an in-place update bumps the version counter
+    K2c.mul_(0.5)
+    assert not _cabi.diag_is_cached(ws, K2c)
+    vp3 = ops._forward_sub_fwd(K2c, V2.cuda(), check=True)
+    assert orc.rel_err(vp3, orc.forward_sub_blockwise(K2c.cpu(), V2)) < 0.01
