@@ -47,6 +47,10 @@ extern "C" {
 #define LUCID_E_NULL_POINTER (-5)
 #define LUCID_E_TENSOR_MAP (-6)
 #define LUCID_E_NO_DEVICE (-7)
+#define LUCID_E_STATIC_SCRATCH_TOO_SMALL (-8)
+
+/* Size of the scratch array that lucid_fwd_sub_static() keeps inside the library (per GPU). */
+#define LUCID_STATIC_SCRATCH_BYTES (9u << 20)
 
 /* Bytes of scratch the calls below need for a (B, N, H, 128) problem.  The workspace holds the
  * inter-block flags, the scheduler's control words, the per-block unit-triangular inverses
@@ -63,6 +67,36 @@ int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_s
                   const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D, int dtype,
                   int flags, int window_blocks, int chain_group, void* workspace, size_t workspace_bytes,
                   void* cuda_stream);
+
+/* The forward solve for callers that must not allocate device memory.
+ *
+ * This entry point has no counterpart in the reference (whose interface allocates its flags, timestamps
+ * and diagonal inverses with torch on every call).  It exists for hosts that drive the solve from a
+ * context where cudaMalloc is off limits: a real-time or latency-critical serving loop that has frozen
+ * its memory plan, a plugin called while another component owns the allocator, code running under a
+ * memory-pool policy that forbids growth, or a process that has already handed all device memory to a
+ * framework.  Such a caller still passes k, v and v_prime, but no workspace: the flags, control words,
+ * per-block unit-triangular inverses and row scales go into an array that is part of the library's own
+ * device image (LUCID_STATIC_SCRATCH_BYTES = 9 MiB, held by every GPU that loads the library until the
+ * process exits).  The call path performs no cudaMalloc, cudaFree or allocating library call.
+ *
+ * Limits and rules:
+ *  - the problem must fit the array: lucid_workspace_bytes(B, N, H) <= 9 MiB minus alignment, i.e. up to
+ *    B*H*N = 32768 rows (for example B=1, H=2, N=16384, or B=2, H=4, N=4096); larger problems are refused
+ *    with LUCID_E_STATIC_SCRATCH_TOO_SMALL and nothing is launched;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *    first call outside any stream capture;
+ *  - all calls on a device share the one array, so two calls that can overlap on the GPU (different
+ *    streams, or host threads) race with each other: serialise them;
+ *  - the array keeps the previous call's contents; the call clears what must start at zero (flags and
+ *    control words) itself and always recomputes the diagonal inverses (LUCID_FLAG_REUSE_DIAG is ignored);
+ *  - status_out may be NULL (nothing synchronises); if it is not, the call synchronises cuda_stream and
+ *    fills it exactly like lucid_read_status().
+ * All other arguments are those of lucid_fwd_sub. */
+int lucid_fwd_sub_static(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D,
+                         int dtype, int flags, int window_blocks, int chain_group, void* cuda_stream,
+                         int32_t status_out[8]);
 
 /* dV = L^-T dV' and, in LUCID_BWD_COMBINED mode, dK.  Replaces _forward_sub_bwd
  * (forward_sub_interface.py:357-378): _compute_diag_inv_transpose (:177-193), the BackwardSubSm90

@@ -28,7 +28,7 @@ _I64x3 = ctypes.c_int64 * 3
 
 EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_read_status",
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
-           "lucid_profile_next_call", "lucid_set_group_overlap")
+           "lucid_profile_next_call", "lucid_set_group_overlap", "lucid_fwd_sub_static")
 
 
 class LucidKernelError(RuntimeError):
@@ -61,6 +61,10 @@ def load() -> ctypes.CDLL:
         lib.lucid_fwd_sub.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, _I64x3, _I64x3, _I64x3,
                                       c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
                                       c.c_void_p, c.c_size_t, c.c_void_p]
+        lib.lucid_fwd_sub_static.restype = c.c_int
+        lib.lucid_fwd_sub_static.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, _I64x3, _I64x3, _I64x3,
+                                             c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                                             c.c_int, c.c_void_p, c.POINTER(c.c_int32)]
         lib.lucid_bwd_sub.restype = c.c_int
         lib.lucid_bwd_sub.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
                                       _I64x3, _I64x3, _I64x3, _I64x3, _I64x3,

@@ -214,6 +214,45 @@ int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_s
   return rc;
 }
 
+// ---- forward solve on library-owned scratch (no allocation anywhere on the call path) ----------------
+// The scratch lives in the library's device image: every GPU that loads the library carries these 9 MiB
+// until the process exits.  Host code may not use the array's name as a pointer; its device address is
+// fetched once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[LUCID_STATIC_SCRATCH_BYTES];
+static unsigned char* g_static_scratch_ptr[64] = {nullptr};
+
+int lucid_fwd_sub_static(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D,
+                         int dtype, int flags, int window_blocks, int chain_group, void* cuda_stream,
+                         int32_t status_out[8]) {
+  int rc;
+  if ((rc = check_shape(B, N, H, D, dtype))) return rc;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return LUCID_E_NO_DEVICE;
+  if (!g_static_scratch_ptr[dev]) {
+    // first call on this device: resolve the device address of the array (do this before any capture)
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_scratch_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  // the kernels want a 1 KiB aligned base; the array is only guaranteed 256-byte alignment
+  uintptr_t base = reinterpret_cast<uintptr_t>(g_static_scratch_ptr[dev]);
+  const uintptr_t aligned = (base + 1023) & ~uintptr_t(1023);
+  const size_t usable = LUCID_STATIC_SCRATCH_BYTES - (aligned - base);
+  const size_t need = make_layout(B, N, H).total;
+  if (need > usable) return LUCID_E_STATIC_SCRATCH_TOO_SMALL;
+  // the array still holds whatever the previous call left: never trust a cached inverse in it
+  flags &= ~LUCID_FLAG_REUSE_DIAG;
+  rc = lucid_fwd_sub(k, v, v_prime, k_strides, v_strides, vp_strides, B, N, H, D, dtype, flags, window_blocks,
+                     chain_group, reinterpret_cast<void*>(aligned), usable, cuda_stream);
+  if (rc) return rc;
+  if (status_out) return lucid_read_status(reinterpret_cast<void*>(aligned), cuda_stream, status_out);
+  return 0;
+}
+
 int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void* dv, void* dk,
                   const int64_t k_strides[3], const int64_t vp_strides[3], const int64_t dvp_strides[3],
                   const int64_t dv_strides[3], const int64_t dk_strides[3], int B, int N, int H, int D, int dtype,
@@ -300,6 +339,8 @@ const char* lucid_status_string(int code) {
     case LUCID_E_NULL_POINTER: return "null pointer";
     case LUCID_E_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected a tensor";
     case LUCID_E_NO_DEVICE: return "no CUDA device";
+    case LUCID_E_STATIC_SCRATCH_TOO_SMALL:
+      return "problem too large for the library-owned scratch of lucid_fwd_sub_static (9 MiB: B*H*N <= 32768 rows)";
     default: return code > 0 ? "CUDA runtime error" : "unknown";
   }
 }

@@ -1,0 +1,73 @@
+"""The allocation-free forward entry point, `lucid_fwd_sub_static`.
+
+Some hosts cannot call cudaMalloc at the moment they need the solve: a serving loop that froze its
+memory plan at start-up, a plugin running while another component owns the allocator, a process whose
+device memory is already fully handed to a framework pool.  For them the library carries its own 9 MiB
+scratch array; the caller passes only k, v and the output.  This test drives that entry point through
+the C ABI (ctypes) and checks it against the regular entry point, twice in a row with different inputs
+so that anything the first call left in the shared array would show up in the second.
+
+Collected last on purpose (file name): a failure here cannot hide the other tests' results.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import lucid_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _static_fwd(lib, k, v, flags=1, window=0):
+    from lucid_kernels_b200 import _cabi
+
+    B, N, H, D = k.shape
+    out = torch.empty_like(v)
+    status = (ctypes.c_int32 * 8)()
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    rc = lib.lucid_fwd_sub_static(k.data_ptr(), v.data_ptr(), out.data_ptr(), _cabi.strides3(k), _cabi.strides3(v),
+                                  _cabi.strides3(out), B, N, H, D, _cabi.dtype_code(k.dtype), flags, window, 0,
+                                  torch.cuda.current_stream().cuda_stream, status)
+    # driver-level free memory: the call itself must not have taken any device memory
+    _static_fwd.taken = free_before - torch.cuda.mem_get_info()[0]
+    return rc, out, list(status)
+
+
+def test_static_scratch_forward_matches_regular_entry_point():
+    from lucid_kernels_b200 import _cabi
+    from lucid_kernels_b200.cute import _forward_sub_fwd
+
+    lib = _cabi.load()
+    for seed, (B, N, H) in enumerate([(2, 2048, 4), (1, 1024, 3)]):
+        K, V, _ = orc.make_inputs(B, N, H, dtype=torch.bfloat16, seed=40 + seed)
+        Kc, Vc = K.cuda(), V.cuda()
+        ref = _forward_sub_fwd(Kc, Vc, use_diag_solve=True, check=True)
+        torch.cuda.synchronize()
+        rc, out, status = _static_fwd(lib, Kc, Vc)
+        assert rc == 0, lib.lucid_status_string(rc)
+        assert status[0] == 0, status
+        # same kernels on the same inputs: identical bits; the gate below is the parity tolerance
+        assert orc.rel_err(out, ref) < 1e-2
+        assert torch.equal(out, ref)
+        assert orc.rel_err(out, orc.forward_sub_blockwise(K, V)) < 1e-2
+        if seed > 0:
+            # (the very first launch of a kernel may make the driver load its code; later calls take nothing)
+            assert _static_fwd.taken <= 0, _static_fwd.taken
+        del Kc, Vc, ref, out
+
+
+def test_static_scratch_rejects_oversized_problems():
+    from lucid_kernels_b200 import _cabi
+
+    lib = _cabi.load()
+    K, V, _ = orc.make_inputs(1, 128, 1, dtype=torch.bfloat16)
+    Kc, Vc = K.cuda(), V.cuda()
+    # claim a problem far beyond 9 MiB of scratch: must be refused before anything is launched
+    out = torch.empty_like(Vc)
+    rc = lib.lucid_fwd_sub_static(Kc.data_ptr(), Vc.data_ptr(), out.data_ptr(), _cabi.strides3(Kc),
+                                  _cabi.strides3(Vc), _cabi.strides3(out), 2, 32768, 8, 128, 1, 1, 0, 0,
+                                  torch.cuda.current_stream().cuda_stream, None)
+    assert rc == -8
+    assert b"scratch" in lib.lucid_status_string(rc)
