@@ -334,8 +334,11 @@ def main():
         f_dk_local = f_dk * n_local / nsys
         dk_tflops = f_dk_local / (k_ms["bwd_dk"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
+        # DRAM bytes per dk_kernel launch: 254.9 MB measured by ncu at N=16384 with 16 systems (profiles/), equal to the
+        # compulsory bytes (read K, V', dV; write dK), which scale with N and with the systems on this rank
+        traffic = 254.9e6 * (N / 16384.0) * (n_local / 16.0)
         roofline = dict(bound="tensor", kernel="dk_kernel", achieved=dk_tflops, peak=peak, unit="TFLOP/s",
-                        frac=dk_tflops / peak, traffic=None, peak_source=peaks["source"] + " (sustained)",
+                        frac=dk_tflops / peak, traffic=traffic, peak_source=peaks["source"] + " (sustained)",
                         per_kernel_ms=k_ms,
                         per_kernel_tflops=dict(
                             fwd_solve=f_fwd * n_local / nsys / (k_ms["fwd_solve"] * 1e-3) / 1e12,
@@ -351,7 +354,7 @@ def main():
                                 seed=0),
                     frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (world * peaks["bf16_tflops"]),
                     roofline=roofline, clocks=clocks, gpu_launches=4 * args.steps, e2e=e2e)
-        if not args.no_cpu_baseline and world >= 1:
+        if not args.no_cpu_baseline and world == 1:
             cb, _ = cpu_naive_sample()
             line["cpu_baseline"] = cb
         print(json.dumps(line), flush=True)

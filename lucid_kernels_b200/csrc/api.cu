@@ -119,11 +119,12 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
                      const Layout& lay, cudaStream_t stream) {
   const int CT = p.C * p.T;
   Control* ctl = reinterpret_cast<Control*>(ws);
-  CUtensorMap tm_k, tm_in, tm_out, tm_x;
+  CUtensorMap tm_k, tm_in, tm_out, tm_x, tm_st;
   int rc;
   if ((rc = bshd_map(&tm_k, bf16, k, ks, p.B, p.N, p.H, 128))) return rc;
   if ((rc = bshd_map(&tm_in, bf16, in, ins, p.B, p.N, p.H, 128))) return rc;
   if ((rc = bshd_map(&tm_out, bf16, out, outs, p.B, p.N, p.H, 64))) return rc;
+  if ((rc = bshd_map(&tm_st, bf16, out, outs, p.B, p.N, p.H, 128))) return rc;
   {
     uint64_t dims[2] = {(uint64_t)kBlock, (uint64_t)CT * kBlock};
     uint64_t str[1] = {256};
@@ -154,7 +155,7 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
   const int sms = sm_count();
   if (sms <= 0) return LUCID_E_NO_DEVICE;
   const int grid = CT < sms ? CT : sms;
-  if ((e = launch_solve(bf16, reverse, tm_k, tm_in, tm_out, tm_x, sa, grid, stream)) != cudaSuccess) return (int)e;
+  if ((e = launch_solve(bf16, reverse, tm_k, tm_in, tm_out, tm_x, tm_st, sa, grid, stream)) != cudaSuccess) return (int)e;
   record_event(2, stream);
   return 0;
 }

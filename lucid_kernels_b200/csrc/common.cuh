@@ -77,16 +77,20 @@ __device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, vol
   return true;
 }
 
-// Wait until flag != 0 (acquire).  Polls the global status word so that one CTA's failure releases
-// every waiter.  Returns the nanoseconds spent waiting through *waited when it is non-null.
+// A row-block is published by eight warps, each adding 1 to its flag with release semantics after its
+// own stores; the block is complete when the flag reaches kFlagComplete.
+constexpr int kFlagComplete = 8;
+
+// Wait until the flag reaches kFlagComplete (acquire).  Polls the global status word so that one CTA's
+// failure releases every waiter.  Returns the nanoseconds spent waiting through *waited when non-null.
 __device__ __forceinline__ bool wait_flag(const int* flag, volatile int* cta_abort, Control* ctl,
                                           unsigned long long limit_ns, int chain, int row, int dep_row,
                                           unsigned long long* waited) {
-  if (ld_acquire_gpu(flag) != 0) return true;
+  if (ld_acquire_gpu(flag) >= kFlagComplete) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   bool ok = true;
-  while (ld_acquire_gpu(flag) == 0) {
+  while (ld_acquire_gpu(flag) < kFlagComplete) {
     if ((++spins & 63u) == 0) {
       if (*cta_abort) { ok = false; break; }
       if (ld_relaxed_gpu(&ctl->status[0]) != 0) {
@@ -101,7 +105,6 @@ __device__ __forceinline__ bool wait_flag(const int* flag, volatile int* cta_abo
         break;
       }
     }
-    __nanosleep(20);
   }
   if (waited) *waited += globaltimer_ns() - t0;
   return ok;

@@ -352,8 +352,7 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
           uint32_t sv[32];
           tmem_ld32(s_tmem + c * 32, sv);
           tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) ev[c * 32 + e] = -ex2_approx(__uint_as_float(sv[e]) * kLog2e);
+          neg_exp2_f32x32(sv, kLog2e, &ev[c * 32]);
         }
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
         // Diagonal tiles keep c <= r (D1, the last lower tile) or c >= r (D2, the first upper tile):
@@ -385,7 +384,7 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
           for (int e = 0; e < 16; ++e) {
             const float w0 = ev[c * 32 + 2 * e] * __uint_as_float(gv[2 * e]);
             const float w1 = ev[c * 32 + 2 * e + 1] * __uint_as_float(gv[2 * e + 1]);
-            pk[e] = pack2<kBf16>(w0, w1);
+            pk[e] = pack2_fast<kBf16>(w0, w1);
           }
           tmem_st16(s_tmem + c * 16, pk);   // this group's W half sits at columns 64*wg .. 64*wg+31
           if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 45 + 2 * c, gq);

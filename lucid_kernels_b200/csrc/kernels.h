@@ -32,8 +32,8 @@ struct DkArgs {
 };
 
 cudaError_t launch_solve(bool bf16, bool reverse, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
-                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const SolveArgs& args, int grid,
-                         cudaStream_t stream);
+                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const CUtensorMap& tm_st,
+                         const SolveArgs& args, int grid, cudaStream_t stream);
 cudaError_t launch_diag_prep(bool bf16, const CUtensorMap& tm_k, const PrepArgs& args, int nblocks,
                              cudaStream_t stream);
 cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,

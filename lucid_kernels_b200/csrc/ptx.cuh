@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace lucid {
@@ -91,6 +92,9 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 __device__ __forceinline__ void st_release_gpu(int* p, int v) {
   asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
   int v;
   asm volatile("ld.relaxed.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -117,6 +121,19 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+
+// TMA tiled store shared -> global (bulk async-group completion)
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed stores have finished READING shared memory (the buffer may be reused)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all committed stores are complete (their writes have been performed)
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // TMEM allocation (one full warp executes these)
@@ -258,6 +275,28 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two exponentials per MUFU instruction: 2^x for a pair of values through ex2.approx.f16x2.  The
+// MUFU pipe issues 16 results per clock per SM for fp32 and as many *instructions* for f16x2, so this
+// halves the MUFU time of a 128 x 128 tile (16384 exponentials) from 1024 to 512 cycles.  Accuracy: x is
+// rounded to fp16 (11 significant bits) first, a relative error of the result of at most 2^-11 * ln2 * |x|
+// rounded up to a power of two: 3.4e-4 for |x| < 2, 1.4e-3 for |x| < 8, below or at the size of the bf16
+// rounding the result undergoes anyway.  Range: results above 65504 (x >= 16) overflow and results below
+// 6e-8 vanish, so callers route any group of values whose maximum is not below 15.9 through
+// the fp32 instruction instead.  Measured on B200 (B=2, N=32768, H=8): 11 % slower than the fp32
+// instruction in both kernels (the guard and the extra conversions cost more than the MUFU time saved),
+// so it is off by default.
+__device__ __forceinline__ uint32_t ex2_f16x2(float x_lo, float x_hi) {
+  uint32_t xh, r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(xh) : "f"(x_hi), "f"(x_lo));
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(xh));
+  return r;
+}
+#ifndef LUCID_EXP_F16X2
+#define LUCID_EXP_F16X2 0
+#endif
+constexpr bool kExpF16x2 = LUCID_EXP_F16X2 != 0;
+constexpr float kExpF16x2Max = 15.9f;
+
 // 2^x on the FMA and ALU pipes, for use beside ex2.approx when the MUFU pipe (16 results per clock per
 // SM) is the bottleneck.  Cody-Waite split: adding 1.5 * 2^23 rounds x to the nearest integer n in the
 // low mantissa bits; 2^f for f = x - n in [-0.5, 0.5] is a degree-3 minimax polynomial (max relative
@@ -297,6 +336,26 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
   return r;
 }
+// The same packing for bf16 done with integer instructions: add half an ulp of the 16-bit result to the
+// fp32 bit pattern (round to nearest, ties away from zero; infinities stay infinities) and splice the two
+// upper halves with one byte permute.  Used in the exp loops, where the conversion instruction would
+// compete with ex2 for the MUFU pipe.  Measured on B200: no gain (dK kernel 3 % slower), so off by default.
+#ifndef LUCID_PACK_ALU
+#define LUCID_PACK_ALU 0
+#endif
+__device__ __forceinline__ uint32_t pack2_bf16_alu(float lo, float hi) {
+  const uint32_t a = __float_as_uint(lo) + 0x8000u;
+  const uint32_t b = __float_as_uint(hi) + 0x8000u;
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2_fast(float lo, float hi) {
+  if constexpr (kBf16 && (LUCID_PACK_ALU != 0)) return pack2_bf16_alu(lo, hi);
+  else return pack2<kBf16>(lo, hi);
+}
+
 template <bool kBf16>
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
   float2 f;
@@ -308,6 +367,63 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
     f = __half22float2(h);
   }
   return f;
+}
+
+// exp2 of 32 consecutive values (given as fp32 bit patterns, to be multiplied by `scale` first) packed
+// into 16 words of bf16 or fp16 pairs, optionally negated.  Uses the paired fp16 instruction unless the
+// largest argument is too big for an fp16 result.
+template <bool kBf16, bool kNegate>
+__device__ __forceinline__ void exp2_pack32(const uint32_t* v, float scale, uint32_t (&pk)[16]) {
+  if constexpr (kExpF16x2) {
+    float m = __uint_as_float(v[0]);
+#pragma unroll
+    for (int e = 1; e < 32; ++e) m = fmaxf(m, __uint_as_float(v[e]));
+    if (m * scale < kExpF16x2Max) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        uint32_t h = ex2_f16x2(__uint_as_float(v[2 * e]) * scale, __uint_as_float(v[2 * e + 1]) * scale);
+        if constexpr (kNegate) h ^= 0x80008000u;
+        if constexpr (kBf16) {
+          const float2 f = unpack2<false>(h);
+          pk[e] = pack2<true>(f.x, f.y);
+        } else {
+          pk[e] = h;
+        }
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    float e0 = ex2_mixed(__uint_as_float(v[2 * e]) * scale, 2 * e);
+    float e1 = ex2_mixed(__uint_as_float(v[2 * e + 1]) * scale, 2 * e + 1);
+    if constexpr (kNegate) {
+      e0 = -e0;
+      e1 = -e1;
+    }
+    pk[e] = pack2_fast<kBf16>(e0, e1);
+  }
+}
+
+// -2^(v * scale) for 32 consecutive values, kept in fp32 (same fp16-pair shortcut and guard as above).
+__device__ __forceinline__ void neg_exp2_f32x32(const uint32_t* v, float scale, float* out) {
+  if constexpr (kExpF16x2) {
+    float m = __uint_as_float(v[0]);
+#pragma unroll
+    for (int e = 1; e < 32; ++e) m = fmaxf(m, __uint_as_float(v[e]));
+    if (m * scale < kExpF16x2Max) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const uint32_t h = ex2_f16x2(__uint_as_float(v[2 * e]) * scale, __uint_as_float(v[2 * e + 1]) * scale) ^ 0x80008000u;
+        const float2 f = unpack2<false>(h);
+        out[2 * e] = f.x;
+        out[2 * e + 1] = f.y;
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 32; ++e) out[e] = -ex2_approx(__uint_as_float(v[e]) * scale);
 }
 
 // Byte offset of 16-byte chunk `chunk` (0..7 within a 64-element panel) of row `row` inside a

@@ -8,8 +8,8 @@
 // from shared memory), P = exp(S) on the TMEM -> register path, and ACC += P * Y_j with P fed back
 // from TMEM (Y = V' forward, dV reverse).  The row-block then forms rhs = Y_in_i - ACC, applies the
 // unit-triangular inverse X_i (precomputed by diag_prep.cu) as one more MMA together with the row
-// scaling exp(-|k_r|^2), stores Y_i and publishes flag[chain][i] with release semantics.  Consumers
-// acquire the flag before their TMA load of Y_i.
+// scaling exp(-|k_r|^2), stores Y_i and publishes it by raising flag[chain][i] with release semantics (one
+// increment per storing warp).  Consumers acquire the complete flag before their TMA load of Y_i.
 //
 // Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 issues the
 // S products and owns TMEM, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warp 3 issues the
@@ -29,9 +29,9 @@ struct SolveSmem {
   alignas(1024) uint8_t vring[4][kHalfBytes];  // Y_j row halves (2 panels x 64 rows x 64 columns)
   alignas(8) uint64_t k_full[4];
   uint64_t k_empty[4], v_full[4], v_empty[4];
-  uint64_t ki_full, ki_free, x_full, vi_full, xr_free;
+  uint64_t ki_full, ki_free, x_full, vi_full, xr_free, r_free, stage_full;
   uint64_t s_full[2], s_free[2], p_full[2], p_free[2];
-  uint64_t acc_full, acc_free, rhs_full, out_full, pub;
+  uint64_t acc_full, acc_free, rhs_full, out_full;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
   uint32_t tmem_base;
@@ -41,7 +41,7 @@ struct SolveSmem {
 enum SolveBar : int {
   BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
   BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
-  BAR_TK_EMPTY, BAR_PUB, BAR_S_FREE, BAR_P_FREE
+  BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL
 };
 
 constexpr int kSolveThreads = 384;
@@ -59,6 +59,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
              const __grid_constant__ CUtensorMap tm_in,    // V (or dV'), box 64 x 128
              const __grid_constant__ CUtensorMap tm_out,   // Y, box 64 x 64
              const __grid_constant__ CUtensorMap tm_x,     // X workspace (2D), box 64 x 128
+             const __grid_constant__ CUtensorMap tm_st,    // Y again, box 64 x 128, for the TMA store of Y_i
              const SolveArgs args) {
   extern __shared__ uint8_t smem_raw[];
   SolveSmem& s = *reinterpret_cast<SolveSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -81,6 +82,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     mbar_init(&s.x_full, 1);
     mbar_init(&s.vi_full, 1);
     mbar_init(&s.xr_free, 1);
+    mbar_init(&s.r_free, 1);
+    mbar_init(&s.stage_full, 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.s_full[i], 1);
       mbar_init(&s.s_free[i], 128);
@@ -93,7 +96,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     mbar_init(&s.acc_free, 256);
     mbar_init(&s.rhs_full, 256);
     mbar_init(&s.out_full, 1);
-    mbar_init(&s.pub, 256);
     s.abort_flag = 0;
     mbar_fence_init();
   }
@@ -209,7 +211,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         unsigned long long waited = 0;
         for (int q = 0; q < n && alive; ++q) {
           const int j = tile_j(jfirst, q);
-          if (!vi_loaded && mbar_try_wait(&s.xr_free, (it & 1) ^ 1)) load_vi();
+          if (!vi_loaded && mbar_try_wait(&s.r_free, (it & 1) ^ 1)) load_vi();
           if (!P.no_sync) {
             if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j,
                            P.instrument ? &waited : nullptr)) {
@@ -232,7 +234,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
           }
         }
         if (alive && !vi_loaded) {
-          if (!wait_barrier(&s.xr_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_XR_FREE)) break;
+          if (!wait_barrier(&s.r_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_R_FREE)) break;
           load_vi();
         }
         if (P.instrument && args.timestamps) args.timestamps[(chain * T + i) * 8 + 3] = (long long)waited;
@@ -384,6 +386,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
           if (leader) LUCID_TR(args.trace, 5, trc, 37, 0);
         } else {
           mbar_arrive_w(&s.xr_free);
+          mbar_arrive_w(&s.r_free);
         }
       }
     }
@@ -449,12 +452,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float e0 = ex2_mixed(__uint_as_float(v[c * 32 + 2 * e]) * kLog2e, c * 32 + 2 * e);
-            const float e1 = ex2_mixed(__uint_as_float(v[c * 32 + 2 * e + 1]) * kLog2e, c * 32 + 2 * e + 1);
-            pk[e] = pack2<kBf16>(e0, e1);
-          }
+          exp2_pack32<kBf16, false>(&v[c * 32], kLog2e, pk);
           tmem_st16(p_tmem + c * 16, pk);
         }
         tmem_wait_st();
@@ -466,23 +464,29 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       g += n;
 
       // ---- epilogue: this group owns output columns 64*wg .. 64*wg+63 ----
-      float acc[64];
+      // Everything that does not depend on the accumulator is done before waiting for it: this
+      // row-block's own right-hand side is read from shared memory now.
+      if (!wait_barrier(&s.vi_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_VI_FULL)) break;
+      uint8_t* panel = s.rhs + wg * kHalfBytes;
+      uint4 vin[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) vin[c] = *reinterpret_cast<const uint4*>(panel + sw128_off(row, c));
+      const float pre = (P.use_diag && !kReverse) ? lam : 1.0f;   // forward: rows scaled before X
+      const float post = (P.use_diag && kReverse) ? lam : 1.0f;   // reverse: rows scaled after X^T
+      typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
+      elem_t* out_row = reinterpret_cast<elem_t*>(args.out) + (long long)b * args.out_strides.b +
+                        (long long)(i * kBlock + row) * args.out_strides.n + (long long)h * args.out_strides.h +
+                        wg * 64;
+      uint32_t acc[64];
+      if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FULL)) break;
       if (n > 0) {
-        if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FULL)) break;
         tc_fence_after_sync();
-        uint32_t v[32];
-        tmem_ld32(lane_base + kTmemAcc + wg * 64, v);
+        tmem_ld32(lane_base + kTmemAcc + wg * 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+        tmem_ld32(lane_base + kTmemAcc + wg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
         tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(v[e]);
-        tmem_ld32(lane_base + kTmemAcc + wg * 64 + 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) acc[32 + e] = __uint_as_float(v[e]);
       } else {
-        if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FULL)) break;
 #pragma unroll
-        for (int e = 0; e < 64; ++e) acc[e] = 0.f;
+        for (int e = 0; e < 64; ++e) acc[e] = 0u;
       }
       // The diagonal product is written over the accumulator, so with use_diag the accumulator is
       // released only after that product has been read back (below).
@@ -493,30 +497,19 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 42, n);
       long long t_loop = 0;
       if (P.instrument && tid == 128) t_loop = (long long)globaltimer_ns();
-
-      if (!wait_barrier(&s.vi_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_VI_FULL)) break;
-      uint8_t* panel = s.rhs + wg * kHalfBytes;
-      const float pre = (P.use_diag && !kReverse) ? lam : 1.0f;   // forward: rows scaled before X
-      const float post = (P.use_diag && kReverse) ? lam : 1.0f;   // reverse: rows scaled after X^T
-      typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
-      elem_t* out_row = reinterpret_cast<elem_t*>(args.out) + (long long)b * args.out_strides.b +
-                        (long long)(i * kBlock + row) * args.out_strides.n + (long long)h * args.out_strides.h +
-                        wg * 64;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        uint4* p = reinterpret_cast<uint4*>(panel + sw128_off(row, c));
-        uint4 w = *p;
-        uint32_t in[4] = {w.x, w.y, w.z, w.w};
+        const uint32_t in[4] = {vin[c].x, vin[c].y, vin[c].z, vin[c].w};
         uint32_t o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 f = unpack2<kBf16>(in[e]);
-          const float r0 = (f.x - acc[c * 8 + 2 * e]) * pre;
-          const float r1 = (f.y - acc[c * 8 + 2 * e + 1]) * pre;
+          const float r0 = (f.x - __uint_as_float(acc[c * 8 + 2 * e])) * pre;
+          const float r1 = (f.y - __uint_as_float(acc[c * 8 + 2 * e + 1])) * pre;
           o[e] = pack2<kBf16>(r0, r1);
         }
         const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-        if (P.use_diag) *p = ov;
+        if (P.use_diag) *reinterpret_cast<uint4*>(panel + sw128_off(row, c)) = ov;
         else *reinterpret_cast<uint4*>(out_row + c * 8) = ov;
       }
       fence_proxy_async_smem();
@@ -528,33 +521,45 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         if (!wait_barrier(&s.out_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_OUT_FULL)) break;
         tc_fence_after_sync();
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 44, 0);
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t v[32];
-          tmem_ld32(lane_base + kTmemOut + wg * 64 + cc * 32, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              o[e] = pack2<kBf16>(__uint_as_float(v[c * 8 + 2 * e]) * post, __uint_as_float(v[c * 8 + 2 * e + 1]) * post);
-            }
-            *reinterpret_cast<uint4*>(out_row + cc * 32 + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        }
+        tmem_ld32(lane_base + kTmemOut + wg * 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+        tmem_ld32(lane_base + kTmemOut + wg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+        tmem_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(&s.acc_free);
+        // Y_i goes back into the rhs buffer (the diagonal product has finished reading it), in the layout
+        // the TMA store expects, and one thread stores the tile, waits for the store to complete and
+        // releases the flag: a single bulk store and a release by a thread with nothing else in flight
+        // publish faster than 256 threads' plain stores followed by GPU-scope fences.
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            o[e] = pack2<kBf16>(__uint_as_float(acc[c * 8 + 2 * e]) * post, __uint_as_float(acc[c * 8 + 2 * e + 1]) * post);
+          }
+          *reinterpret_cast<uint4*>(panel + sw128_off(row, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&s.stage_full);
+        if (tid == 128) {
+          if (!wait_barrier(&s.stage_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_STAGE_FULL)) break;
+          tma_store_4d(&tm_st, s.rhs, 0, i * kBlock, h, b);
+          tma_store_4d(&tm_st, s.rhs + kHalfBytes, 64, i * kBlock, h, b);
+          tma_store_commit();
+          tma_store_wait_read();
+          mbar_arrive(&s.r_free);          // the next row-block's right-hand side may be loaded
+          tma_store_wait_all();
+          fence_proxy_async_all();
+          st_release_gpu(args.flags + chain * T + i, kFlagComplete);
+        }
+      } else {
+        // ---- publish (identity diagonal: the result was stored with plain stores above) ----
+        // Each warp orders its lanes' stores with a warp barrier and then adds 1 to the flag with release
+        // semantics at GPU scope; a consumer that acquires the value 8 observes all eight warps' stores.
+        __syncwarp();
+        if (lane == 0) red_release_gpu_add(args.flags + chain * T + i, 1);
       }
-      // ---- publish ----
-      // Each thread's stores are ordered before its (release) arrival on `pub`; the publishing thread
-      // acquires that barrier and then releases the flag at GPU scope, so that an acquirer of the flag
-      // observes all 256 threads' stores (the consumer orders its TMA read after the acquire with a
-      // proxy fence).
-      mbar_arrive(&s.pub);
       if (tid == 128) {
-        if (!wait_barrier(&s.pub, it & 1, cta_abort, ctl, limit, chain, i, BAR_PUB)) break;
-        st_release_gpu(args.flags + chain * T + i, 1);
         LUCID_TR(args.trace, 3, trc, 45, i);
         if (P.instrument && args.timestamps) {
           long long* ts = args.timestamps + (long long)(chain * T + i) * 8;
@@ -588,23 +593,24 @@ size_t solve_smem_bytes() { return sizeof(SolveSmem) + 1024; }
 
 template <bool kBf16, bool kReverse>
 static cudaError_t launch_solve_t(const CUtensorMap& tm_k, const CUtensorMap& tm_in, const CUtensorMap& tm_out,
-                                  const CUtensorMap& tm_x, const SolveArgs& args, int grid, cudaStream_t stream) {
+                                  const CUtensorMap& tm_x, const CUtensorMap& tm_st, const SolveArgs& args, int grid,
+                                  cudaStream_t stream) {
   auto kern = solve_kernel<kBf16, kReverse>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem_bytes());
   if (e != cudaSuccess) return e;
-  kern<<<grid, kSolveThreads, solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, args);
+  kern<<<grid, kSolveThreads, solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
   return cudaGetLastError();
 }
 
 cudaError_t launch_solve(bool bf16, bool reverse, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
-                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const SolveArgs& args, int grid,
-                         cudaStream_t stream) {
+                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const CUtensorMap& tm_st,
+                         const SolveArgs& args, int grid, cudaStream_t stream) {
   if (bf16) {
-    return reverse ? launch_solve_t<true, true>(tm_k, tm_in, tm_out, tm_x, args, grid, stream)
-                   : launch_solve_t<true, false>(tm_k, tm_in, tm_out, tm_x, args, grid, stream);
+    return reverse ? launch_solve_t<true, true>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
+                   : launch_solve_t<true, false>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream);
   }
-  return reverse ? launch_solve_t<false, true>(tm_k, tm_in, tm_out, tm_x, args, grid, stream)
-                 : launch_solve_t<false, false>(tm_k, tm_in, tm_out, tm_x, args, grid, stream);
+  return reverse ? launch_solve_t<false, true>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
+                 : launch_solve_t<false, false>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream);
 }
 
 }  // namespace lucid
