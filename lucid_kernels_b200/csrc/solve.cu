@@ -212,6 +212,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         for (int q = 0; q < n && alive; ++q) {
           const int j = tile_j(jfirst, q);
           if (!vi_loaded && mbar_try_wait(&s.r_free, (it & 1) ^ 1)) load_vi();
+          // Both ring stages of this tile are claimed before the flag is awaited, so that only the proxy
+          // fence stands between observing the flag and issuing the four loads.
+          const int st0 = u & 3, st1 = (u + 1) & 3;
+          if (!wait_barrier(&s.v_empty[st0], ((u >> 2) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_V_EMPTY) ||
+              !wait_barrier(&s.v_empty[st1], (((u + 1) >> 2) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_V_EMPTY)) {
+            alive = false;
+            break;
+          }
           if (!P.no_sync) {
             if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j,
                            P.instrument ? &waited : nullptr)) {
@@ -221,17 +229,14 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
             fence_proxy_async_all();   // flag acquired in the generic proxy; the tile is read by TMA
           }
           LUCID_TR(args.trace, 1, trc, 20, q);
-          for (int half = 0; half < 2; ++half, ++u) {
-            const int st = u & 3;
-            if (!wait_barrier(&s.v_empty[st], ((u >> 2) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_V_EMPTY)) {
-              alive = false;
-              break;
-            }
-            mbar_expect_tx(&s.v_full[st], kHalfBytes);
-            tma_load_4d(s.vring[st], &tm_out, &s.v_full[st], 0, j * kBlock + 64 * half, h, b);
-            tma_load_4d(s.vring[st] + 8192, &tm_out, &s.v_full[st], 64, j * kBlock + 64 * half, h, b);
-            LUCID_TR(args.trace, 1, trc, 21, u);
-          }
+          mbar_expect_tx(&s.v_full[st0], kHalfBytes);
+          tma_load_4d(s.vring[st0], &tm_out, &s.v_full[st0], 0, j * kBlock, h, b);
+          tma_load_4d(s.vring[st0] + 8192, &tm_out, &s.v_full[st0], 64, j * kBlock, h, b);
+          mbar_expect_tx(&s.v_full[st1], kHalfBytes);
+          tma_load_4d(s.vring[st1], &tm_out, &s.v_full[st1], 0, j * kBlock + 64, h, b);
+          tma_load_4d(s.vring[st1] + 8192, &tm_out, &s.v_full[st1], 64, j * kBlock + 64, h, b);
+          LUCID_TR(args.trace, 1, trc, 21, u);
+          u += 2;
         }
         if (alive && !vi_loaded) {
           if (!wait_barrier(&s.r_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_R_FREE)) break;
