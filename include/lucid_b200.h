@@ -121,12 +121,12 @@ const char* lucid_status_string(int code);
 /* Sets the time limit (nanoseconds) of every device-side wait; default 2e9. */
 void lucid_set_wait_limit_ns(uint64_t ns);
 
-/* Scheduler knob: how many of a chain group's first (short, latency-bound) row-blocks are interleaved with
- * the last row-blocks of the previous group (at most T/2); negative restores the default (0: measured
- * slower on B200 whenever enabled, kept as an experiment knob).  No
- * counterpart in the reference, whose grid is one CTA per row-block in launch order
- * (tile_scheduler.py:105-117). */
-void lucid_set_group_overlap(int steps);
+/* Scheduler knob: the first `steps` row-blocks of every (batch, head) system are scheduled for all systems
+ * together (they are short and bound by the hand-over latency between consecutive row-blocks), the rest in
+ * groups of `chain_group` systems; negative restores the default (0, i.e. groups from the start: the
+ * head phase did not pay off in measurements and is kept as an experiment knob).  No counterpart in the reference,
+ * whose grid is one CTA per row-block in launch order (tile_scheduler.py:105-117). */
+void lucid_set_head_steps(int steps);
 
 /* Per-kernel timing for benchmarks: the NEXT lucid_fwd_sub / lucid_bwd_sub call records these
  * cudaEvent_t handles on its stream (before the diagonal-prep kernel, after it, after the solve kernel,

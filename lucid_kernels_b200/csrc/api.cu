@@ -12,7 +12,7 @@ static unsigned long long g_wait_ns = 2000000000ull;
 // optional per-kernel timing: events recorded around the kernels of the NEXT call, then forgotten
 static cudaEvent_t g_events[4] = {nullptr, nullptr, nullptr, nullptr};
 static long long* g_trace = nullptr;
-static int g_overlap = -1;   // scheduler knob for experiments; < 0 = default
+static int g_head = -1;   // scheduler knob; < 0 = default
 static inline void record_event(int i, cudaStream_t stream) {
   if (g_events[i]) cudaEventRecord(g_events[i], stream);
 }
@@ -99,11 +99,12 @@ static Problem make_problem(int B, int N, int H, int flags, int window, int grou
   p.T = N / kBlock;
   p.C = B * H;
   p.group = auto_group(p.C, N, group);
-  // Optional interleaving of the latency-bound first steps of a group with the end of the previous one.
-  // Off by default: on B=2, N=32768, H=8 the forward took 4.71 / 4.85 / 5.29 / 5.35 ms with 0 / 32 / 64 / 96
-  // steps interleaved, because two groups' tiles then compete for the L2.
-  p.overlap = g_overlap >= 0 ? g_overlap : 0;
-  if (2 * p.overlap > p.T) p.overlap = p.T / 2;
+  // Optionally the short, latency-bound first row-blocks of every chain are scheduled for all chains
+  // together before the groups start.  Off by default: on B=2, N=32768, H=8 a sweep over 0 / 48 / 96 / 144 /
+  // 192 / 256 steps gave 4.7-5.9 / 5.0-5.2 / 5.1-5.2 / 5.2-5.4 / 5.5 / 6.1 ms for the forward, i.e. no gain
+  // beyond run-to-run noise and a loss once the head is long.
+  p.head = g_head >= 0 ? g_head : 0;
+  if (p.head > p.T) p.head = p.T;
   p.use_diag = (flags & LUCID_FLAG_DIAG_SOLVE) ? 1 : 0;
   p.window = window;
   p.no_sync = (flags & LUCID_FLAG_NO_SYNC) ? 1 : 0;
@@ -178,7 +179,7 @@ size_t lucid_workspace_timestamps_offset(int B, int N, int H) {
 
 void lucid_set_wait_limit_ns(uint64_t ns) { g_wait_ns = ns; }
 
-void lucid_set_group_overlap(int steps) { g_overlap = steps; }
+void lucid_set_head_steps(int steps) { g_head = steps; }
 
 #ifdef LUCID_TRACE
 void lucid_debug_set_trace(void* buf) { g_trace = static_cast<long long*>(buf); }

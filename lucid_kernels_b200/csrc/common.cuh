@@ -35,7 +35,7 @@ struct Problem {
   int B, N, H, T;    // T = N / 128
   int C;             // chains = B * H
   int group;         // chains advanced together by the scheduler
-  int overlap;       // steps of the next group interleaved with the end of the current one (2*overlap <= T)
+  int head;          // leading steps that are scheduled for all chains together before the groups start
   int use_diag;      // apply the diagonal-block solve
   int window;        // forward only: number of previous blocks used (<= 0: all)
   int no_sync;       // skip flag waits (profiling only; results are then meaningless)
@@ -110,58 +110,32 @@ __device__ __forceinline__ bool wait_flag(const int* flag, volatile int* cta_abo
   return ok;
 }
 
-// Work item t -> (chain, step).  Chains are advanced in groups of `group` (sized so that a group's K and
-// Y stay in the L2); inside a group the order is step-major, so an item's predecessors (same chain,
-// smaller step) always have smaller tickets.  The first `overlap` steps of group g+1, which are short and
-// bound by the chain latency rather than by throughput, are interleaved with the last `overlap` steps of
-// group g, so that the machine stays busy while the next group ramps up.  Sequence of segments:
-//   solo(0) | mixed(0,1) | solo(1) | mixed(1,2) | ... | solo(last)
-// with solo(g) = steps [g ? overlap : 0, last ? T : T - overlap) of group g, and mixed(g-1, g) = for
-// x in [0, overlap): step T - overlap + x of group g-1, then step x of group g.
-__device__ __forceinline__ bool decode_ticket(int t, int C, int T, int group, int overlap, int& chain, int& step) {
+// Work item t -> (chain, step).  The first `head` steps of ALL chains come first, step-major: those
+// row-blocks are short, their chains advance at the pace of the hand-over latency rather than of the
+// arithmetic, so as many chains as possible should be in flight, and their K and Y rows are few enough to
+// share the L2.  The remaining steps follow in groups of `group` chains (sized so that a group's K and Y
+// stay in the L2), step-major inside a group.  An item's predecessors (same chain, smaller step) always
+// have smaller tickets.
+__device__ __forceinline__ bool decode_ticket(int t, int C, int T, int group, int head, int& chain, int& step) {
   if (t >= C * T) return false;
-  const int ng = (C + group - 1) / group;
-  if (ng == 1 || overlap <= 0) {
-    const int per = group * T;
-    const int g = t / per;
-    const int base = g * group;
-    const int gsz = min(group, C - base);
-    const int tl = t - g * per;
-    step = tl / gsz;
-    chain = base + tl % gsz;
+  if (head > T) head = T;
+  if (head < 0) head = 0;
+  const int n_head = C * head;
+  if (t < n_head) {
+    step = t / C;
+    chain = t - step * C;
     return true;
   }
-  for (int g = 0; g < ng; ++g) {
-    const int base = g * group;
-    const int gsz = min(group, C - base);
-    if (g > 0) {
-      // mixed segment between group g-1 (full size `group`) and group g
-      const int per_x = group + gsz;
-      const int n_mixed = overlap * per_x;
-      if (t < n_mixed) {
-        const int x = t / per_x, r = t - x * per_x;
-        if (r < group) {
-          step = T - overlap + x;
-          chain = base - group + r;
-        } else {
-          step = x;
-          chain = base + (r - group);
-        }
-        return true;
-      }
-      t -= n_mixed;
-    }
-    const int lo = g ? overlap : 0;
-    const int hi = (g == ng - 1) ? T : T - overlap;
-    const int n_solo = (hi - lo) * gsz;
-    if (t < n_solo) {
-      step = lo + t / gsz;
-      chain = base + t % gsz;
-      return true;
-    }
-    t -= n_solo;
-  }
-  return false;
+  t -= n_head;
+  const int rest = T - head;          // > 0 here
+  const int per = group * rest;
+  const int g = t / per;
+  const int base = g * group;
+  const int gsz = min(group, C - base);
+  const int tl = t - g * per;
+  step = head + tl / gsz;
+  chain = base + tl % gsz;
+  return true;
 }
 
 // Event trace of one CTA (debugging builds only): role r appends {tag, q, clock} triples.

@@ -113,7 +113,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
   // buffers g & 1 in phase (g >> 1) & 1 and is exponentiated by group g & 1.
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& jfirst) -> bool {
     int step;
-    if (!decode_ticket(ticket, P.C, T, P.group, P.overlap, chain, step)) return false;
+    if (!decode_ticket(ticket, P.C, T, P.group, P.head, chain, step)) return false;
     if (kReverse) {
       i = T - 1 - step;
       n = step;           // blocks i+1 .. T-1, visited from T-1 down to i+1
