@@ -141,9 +141,12 @@ __device__ __forceinline__ bool decode_ticket(int t, int C, int T, int group, in
 // Event trace of one CTA (debugging builds only): role r appends {tag, q, clock} triples.
 #ifdef LUCID_TRACE
 constexpr int kTraceMax = 8192;
+#ifndef LUCID_TRACE_ROLES
+#define LUCID_TRACE_ROLES 0xffffffffu       // bit r: role r is traced
+#endif
 #define LUCID_TR(buf, role, cnt, tag, q)                                              \
   do {                                                                                \
-    if ((buf) != nullptr && blockIdx.x == 0 && (cnt) < kTraceMax) {                   \
+    if ((((LUCID_TRACE_ROLES) >> (role)) & 1u) && (buf) != nullptr && blockIdx.x == 0 && (cnt) < kTraceMax) { \
       long long* e_ = (buf) + ((long long)(role) * kTraceMax + (cnt)) * 3;            \
       e_[0] = (tag);                                                                  \
       e_[1] = (q);                                                                    \

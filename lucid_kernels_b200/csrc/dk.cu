@@ -11,10 +11,16 @@
 // with (A, Z) = (dV, V') for the lower part and (V', dV) for the upper part.  Row-blocks are independent:
 // no flags, no ordering; a CTA owns row-block i and streams all T blocks j past it (T + 1 tiles).
 //
-// Warp roles (384 threads): warp 0 producer (tickets, K_i, A_i, K_j ring of 3, Z_j ring of 2), warp 1
-// issues the S and G products and owns TMEM, warp 3 issues the W*K_j products (two issuing warps so that
-// the waits of one overlap the MMAs of the other), warps 4-11 form W: both groups work on the same
-// tile, 64 columns each.
+// Warp roles (384 threads): warp 0 producer (tickets, K_i, A_i, K_j ring of 3, Z_j ring of 2), warps 1, 2
+// and 3 issue the G, S and W*K_j products (one warp per product stream: an issuing thread runs only a
+// few MMAs ahead of the tensor pipe, so a warp that issued two streams would delay the second behind
+// the first), warp 1 owns TMEM, warps 4-11 form W: both groups work on the same tile, 64 columns each.
+//
+// A W-forming thread first pulls its 64 columns of G(q) into registers and releases the single G buffer
+// at once, so that the product G(q+1) runs while W(q) is being formed; it then streams S(q) through in
+// 16-column chunks (the next chunk's TMEM load in flight under the current chunk's arithmetic), forming
+// w = -exp(s) * g in one pass, and writes the packed chunk over S columns it has already consumed.
+// S(q+1) reuses the buffer W(q-1) sat in and is issued as soon as that product has completed.
 #include <type_traits>
 #include "kernels.h"
 
@@ -28,7 +34,7 @@ struct DkSmem {
   alignas(8) uint64_t k_full[3];
   uint64_t k_empty[3], z_full[2], z_empty[2];
   uint64_t ki_full, ki_free, ai_full, ai_free;
-  uint64_t s_full[2], g_full, w_full, w_ready[2], sbuf_free[2];
+  uint64_t s_full[2], g_full, g_free, w_ready[2], sbuf_free[2];
   uint64_t acc_full, acc_free;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
@@ -38,7 +44,7 @@ struct DkSmem {
 
 enum DkBar : int {
   DK_K_FULL = 201, DK_K_EMPTY, DK_Z_FULL, DK_Z_EMPTY, DK_KI_FULL, DK_KI_FREE, DK_AI_FULL, DK_AI_FREE, DK_S_FULL,
-  DK_G_FULL, DK_W_FULL, DK_ACC_FULL, DK_ACC_FREE, DK_TK_FULL, DK_TK_EMPTY, DK_SBUF_FREE, DK_W_READY
+  DK_G_FULL, DK_G_FREE, DK_ACC_FULL, DK_ACC_FREE, DK_TK_FULL, DK_TK_EMPTY, DK_SBUF_FREE, DK_W_READY
 };
 
 constexpr int kDkThreads = 384;
@@ -73,14 +79,14 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
       mbar_init(&s.sbuf_free[i], 1);
       mbar_init(&s.w_ready[i], 256);
       mbar_init(&s.tk_full[i], 1);
-      mbar_init(&s.tk_empty[i], 10);
+      mbar_init(&s.tk_empty[i], 11);
     }
     mbar_init(&s.ki_full, 1);
     mbar_init(&s.ki_free, 1);
     mbar_init(&s.ai_full, 1);
     mbar_init(&s.ai_free, 1);
     mbar_init(&s.g_full, 1);
-    mbar_init(&s.w_full, 256);
+    mbar_init(&s.g_free, 256);
     mbar_init(&s.acc_full, 1);
     mbar_init(&s.acc_free, 256);
     s.abort_flag = 0;
@@ -92,6 +98,12 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
   }
   tc_fence_before_sync();
   __syncthreads();
+  // tracing builds: wall time and SM cycles at the start and end of this CTA (role 6) give the SM clock
+  {
+    int slot6 = 4;
+    (void)slot6;
+    if (tid == 0) LUCID_TR(args.trace, 6, slot6, 90, (long long)globaltimer_ns());
+  }
   tc_fence_after_sync();
   const uint32_t tmem = s.tmem_base;
 
@@ -169,87 +181,105 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
       }
     }
   } else if (warp == 1) {
-    // =========================== S and G issuer ===========================
+    // =========================== G issuer (owns TMEM) ===========================
     // Warp-uniform control flow; one elected lane issues tcgen05 instructions and arrivals.
     {
       constexpr int fmt = kBf16 ? 1 : 0;
-      constexpr uint32_t idesc_kk = umma_idesc(fmt, 0, 0, 128, 128);   // S and G: both operands K-major
-      const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
+      constexpr uint32_t idesc_kk = umma_idesc(fmt, 0, 0, 128, 128);   // both operands K-major
       const uint64_t d_ai = umma_smem_desc(smem_u32(s.ai), 16, 1024);
-      const uint64_t d_kr0 = umma_smem_desc(smem_u32(s.kring[0]), 16, 1024);             // stage: + 32 KiB
-      const uint64_t d_zr0 = umma_smem_desc(smem_u32(s.zring[0]), 16, 1024);
+      const uint64_t d_zr0 = umma_smem_desc(smem_u32(s.zring[0]), 16, 1024);             // stage: + 32 KiB
       uint32_t g = 0, swaps = 0;
       bool alive = true;
       int trc = 0;
       (void)trc;
       const bool leader = (lane == 0);
       (void)leader;
-      int chain = -1, i = -1, n = 0, n_low = 0;
-      auto issue_s = [&](uint32_t gq) -> bool {
-        const uint32_t ks = gq % 3;
-        const uint32_t buf = gq & 1;
-        // W of two tiles ago lived in this buffer: its W*K_j product must have completed
-        if (!wait_barrier(&s.sbuf_free[buf], ((gq >> 1) & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_SBUF_FREE))
-          return false;
-        if (leader) LUCID_TR(args.trace, 2, trc, 29, gq);
-        if (!wait_barrier(&s.k_full[ks], (gq / 3) & 1, cta_abort, ctl, limit, chain, i, DK_K_FULL)) return false;
-        tc_fence_after_sync();
-        if (leader) LUCID_TR(args.trace, 2, trc, 30, gq);
-        const uint32_t dst = tmem + (buf ? kDkS1 : kDkS0);
-        const uint64_t db = d_kr0 + ks * (kTileBytes >> 4);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
-          umma_ss_w(dst, d_ki + off, db + off, idesc_kk, k ? 1u : 0u);
-        }
-        umma_commit_w(&s.s_full[buf]);
-        if (leader) LUCID_TR(args.trace, 2, trc, 31, gq);
-        return true;
-      };
-      auto issue_g = [&](uint32_t gq, int q) -> bool {
-        // the A buffer changes from dV_i to V'_i at q == n_low; wait for the load that serves tile q
-        if ((q == 0 && n_low > 0) || (q == n_low && n_low < n)) {
-          if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) return false;
-          ++swaps;
-        }
-        const uint32_t zs = gq & 1;
-        if (!wait_barrier(&s.z_full[zs], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_Z_FULL)) return false;
-        tc_fence_after_sync();
-        if (leader) LUCID_TR(args.trace, 2, trc, 32, gq);
-        const uint64_t db = d_zr0 + zs * (kTileBytes >> 4);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
-          umma_ss_w(tmem + kDkG, d_ai + off, db + off, idesc_kk, k ? 1u : 0u);
-        }
-        umma_commit_w(&s.z_empty[zs]);
-        umma_commit_w(&s.g_full);
-        if (leader) LUCID_TR(args.trace, 2, trc, 33, gq);
-        // last lower tile (or last tile): the A buffer may be overwritten once this product is done
-        if (q == n_low - 1 || q == n - 1) umma_commit_w(&s.ai_free);
-        return true;
-      };
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, DK_TK_FULL)) break;
         const int ticket = s.tk_slot[slot];
         __syncwarp();
         mbar_arrive_w(&s.tk_empty[slot]);
+        int chain, i, n, n_low;
+        if (!item_geometry(ticket, chain, i, n, n_low)) break;
+        for (int q = 0; q < n; ++q) {
+          const uint32_t gq = g + q;
+          // G(gq-1) is in the registers of all 256 threads: the single G buffer is free again
+          if (gq > 0 &&
+              !wait_barrier(&s.g_free, (gq - 1) & 1, cta_abort, ctl, limit, chain, i, DK_G_FREE)) { alive = false; break; }
+          if (leader) LUCID_TR(args.trace, 2, trc, 34, gq);
+          // the A buffer changes from dV_i to V'_i at q == n_low; wait for the load that serves tile q
+          if ((q == 0 && n_low > 0) || (q == n_low && n_low < n)) {
+            if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) { alive = false; break; }
+            ++swaps;
+          }
+          const uint32_t zs = gq & 1;
+          if (!wait_barrier(&s.z_full[zs], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_Z_FULL)) { alive = false; break; }
+          tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 2, trc, 32, gq);
+          const uint64_t db = d_zr0 + zs * (kTileBytes >> 4);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+            umma_ss_w(tmem + kDkG, d_ai + off, db + off, idesc_kk, k ? 1u : 0u);
+          }
+          umma_commit_w(&s.z_empty[zs]);
+          umma_commit_w(&s.g_full);
+          if (leader) LUCID_TR(args.trace, 2, trc, 33, gq);
+          // last lower tile (or last tile): the A buffer may be overwritten once this product is done
+          if (q == n_low - 1 || q == n - 1) umma_commit_w(&s.ai_free);
+        }
+        if (!alive) break;
+        g += n;
+      }
+    }
+  } else if (warp == 2) {
+    // =========================== S issuer ===========================
+    // Runs ahead of the G issuer as far as the two S buffers allow.
+    {
+      constexpr int fmt = kBf16 ? 1 : 0;
+      constexpr uint32_t idesc_kk = umma_idesc(fmt, 0, 0, 128, 128);
+      const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
+      const uint64_t d_kr0 = umma_smem_desc(smem_u32(s.kring[0]), 16, 1024);             // stage: + 32 KiB
+      uint32_t g = 0;
+      bool alive = true;
+      int trc = 0;
+      (void)trc;
+      const bool leader = (lane == 0);
+      (void)leader;
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, DK_TK_FULL)) break;
+        const int ticket = s.tk_slot[slot];
+        __syncwarp();
+        mbar_arrive_w(&s.tk_empty[slot]);
+        int chain, i, n, n_low;
         if (!item_geometry(ticket, chain, i, n, n_low)) break;
         if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, DK_KI_FULL)) break;
         tc_fence_after_sync();
-        if (leader) LUCID_TR(args.trace, 2, trc, 35, n);
-        if (n > 0) {
-          if (!issue_s(g) || !issue_g(g, 0)) break;
-        }
+        if (leader) LUCID_TR(args.trace, 1, trc, 35, n);
         for (int q = 0; q < n; ++q) {
           const uint32_t gq = g + q;
-          if (q + 1 < n && !issue_s(gq + 1)) { alive = false; break; }
-          // G(q) has been read (and W(q) written) by all 256 threads: the G buffer is free again
-          if (!wait_barrier(&s.w_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_W_FULL)) { alive = false; break; }
+          const uint32_t ks = gq % 3;
+          const uint32_t buf = gq & 1;
+          // W of two tiles ago lived in this buffer: its W*K_j product must have completed
+          if (!wait_barrier(&s.sbuf_free[buf], ((gq >> 1) & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_SBUF_FREE)) {
+            alive = false;
+            break;
+          }
+          if (leader) LUCID_TR(args.trace, 1, trc, 29, gq);
+          if (!wait_barrier(&s.k_full[ks], (gq / 3) & 1, cta_abort, ctl, limit, chain, i, DK_K_FULL)) { alive = false; break; }
           tc_fence_after_sync();
-          if (leader) LUCID_TR(args.trace, 2, trc, 34, gq);
-          if (q + 1 < n && !issue_g(gq + 1, q + 1)) { alive = false; break; }
+          if (leader) LUCID_TR(args.trace, 1, trc, 30, gq);
+          const uint32_t dst = tmem + (buf ? kDkS1 : kDkS0);
+          const uint64_t db = d_kr0 + ks * (kTileBytes >> 4);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+            umma_ss_w(dst, d_ki + off, db + off, idesc_kk, k ? 1u : 0u);
+          }
+          umma_commit_w(&s.s_full[buf]);
+          if (leader) LUCID_TR(args.trace, 1, trc, 31, gq);
         }
         if (!alive) break;
         g += n;
@@ -335,65 +365,64 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
       const int b = chain / H, h = chain % H;
       for (int q = 0; q < n; ++q) {
         const uint32_t gq = g + q;
-        // Phase A needs only S: E = -exp(S) for this thread's 64 columns, kept in registers.  It
-        // overlaps the G product, which the tensor pipe can start only after the previous tile's G
-        // has been read.
+        const uint32_t s_tmem = lane_base + ((gq & 1) ? kDkS1 : kDkS0) + wg * 64;
+        const uint32_t g_tmem = lane_base + kDkG + wg * 64;
+        if (!wait_barrier(&s.g_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_G_FULL)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after_sync();
+        uint32_t gv0[32], gv1[32];
+        tmem_ld32(g_tmem, gv0);
+        tmem_ld32(g_tmem + 32, gv1);
         if (!wait_barrier(&s.s_full[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_S_FULL)) {
           alive = false;
           break;
         }
         tc_fence_after_sync();
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 40, gq);
-        const uint32_t s_tmem = lane_base + ((gq & 1) ? kDkS1 : kDkS0) + wg * 64;
-        const uint32_t g_tmem = lane_base + kDkG + wg * 64;
-        float ev[64];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t sv[32];
-          tmem_ld32(s_tmem + c * 32, sv);
-          tmem_wait_ld();
-          neg_exp2_f32x32(sv, kLog2e, &ev[c * 32]);
-        }
+        uint32_t sva[16], svb[16];
+        tmem_ld16(s_tmem, sva);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(&s.g_free);             // to the S/G issuer: G(q) is in registers
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
-        // Diagonal tiles keep c <= r (D1, the last lower tile) or c >= r (D2, the first upper tile):
-        // the mask is applied to E here, once per tile, so that phase B stays branch-free.
+        // Diagonal tiles keep c <= r (D1, the last lower tile) or c >= r (D2, the first upper tile): the
+        // mask is applied to G here, once per tile, so that the chunk loop stays branch-free.
         const int mask_mode = !diag_tiles ? 0 : (q == n_low - 1 ? 1 : (q == n_low ? 2 : 0));
         if (mask_mode) {
 #pragma unroll
-          for (int e = 0; e < 64; ++e) {
-            const int col = wg * 64 + e;
-            const bool keep = (mask_mode == 1) ? (col <= row) : (col >= row);
-            ev[e] = keep ? ev[e] : 0.f;
+          for (int e = 0; e < 32; ++e) {
+            const int c0 = wg * 64 + e, c1 = c0 + 32;
+            const bool keep0 = (mask_mode == 1) ? (c0 <= row) : (c0 >= row);
+            const bool keep1 = (mask_mode == 1) ? (c1 <= row) : (c1 >= row);
+            gv0[e] = keep0 ? gv0[e] : 0u;
+            gv1[e] = keep1 ? gv1[e] : 0u;
           }
         }
-        // Phase B: W = E o G, packed to 16 bits over the S columns.
-        if (!wait_barrier(&s.g_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_G_FULL)) {
-          alive = false;
-          break;
+        // Chunk c: columns 16c .. 16c+15 of this thread's range; its packed W lands on columns
+        // 8c .. 8c+7, inside chunks <= c, which are already in registers.
+#define LUCID_DK_CHUNK(C, CUR, NXT, GV, GOFF)                                                          \
+        {                                                                                              \
+          if ((C) < 3) tmem_ld16(s_tmem + ((C) + 1) * 16, NXT);                                        \
+          uint32_t pk[8];                                                                              \
+          _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                              \
+            const float e0 = ex2_approx(__uint_as_float(CUR[2 * e]) * kLog2e);                         \
+            const float e1 = ex2_approx(__uint_as_float(CUR[2 * e + 1]) * kLog2e);                     \
+            pk[e] = pack2_fast<kBf16>(-e0 * __uint_as_float(GV[(GOFF) + 2 * e]),                       \
+                                      -e1 * __uint_as_float(GV[(GOFF) + 2 * e + 1]));                  \
+          }                                                                                            \
+          if ((C) < 3) tmem_wait_ld();                                                                 \
+          tmem_st8(s_tmem + (C) * 8, pk);                                                              \
         }
-        tc_fence_after_sync();
-        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 42, gq);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t gv[32];
-          tmem_ld32(g_tmem + c * 32, gv);
-          tmem_wait_ld();
-          if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 44 + 2 * c, gq);
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float w0 = ev[c * 32 + 2 * e] * __uint_as_float(gv[2 * e]);
-            const float w1 = ev[c * 32 + 2 * e + 1] * __uint_as_float(gv[2 * e + 1]);
-            pk[e] = pack2_fast<kBf16>(w0, w1);
-          }
-          tmem_st16(s_tmem + c * 16, pk);   // this group's W half sits at columns 64*wg .. 64*wg+31
-          if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 45 + 2 * c, gq);
-        }
+        LUCID_DK_CHUNK(0, sva, svb, gv0, 0)
+        LUCID_DK_CHUNK(1, svb, sva, gv0, 16)
+        LUCID_DK_CHUNK(2, sva, svb, gv1, 0)
+        LUCID_DK_CHUNK(3, svb, sva, gv1, 16)
+#undef LUCID_DK_CHUNK
         tmem_wait_st();
-        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 48, gq);
         tc_fence_before_sync();
-        mbar_arrive(&s.w_full);             // to the S/G issuer: the G buffer has been read
-        mbar_arrive(&s.w_ready[gq & 1]);    // to the W*K_j issuer: W is in place
+        mbar_arrive(&s.w_ready[gq & 1]);    // to the W*K_j issuer: W(q) is in place
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 43, gq);
       }
       if (!alive) break;
@@ -435,6 +464,11 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
     if (tid == 0) report_error(ctl, kErrAborted, -1, -1, blockIdx.x, 0);
   }
   tc_fence_before_sync();
+  {
+    int slot6 = 4 + 1;
+    (void)slot6;
+    if (tid == 0) LUCID_TR(args.trace, 6, slot6, 91, (long long)globaltimer_ns());
+  }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
 }

@@ -105,6 +105,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
   }
   tc_fence_before_sync();
   __syncthreads();
+  // tracing builds: wall time and SM cycles at the start and end of this CTA (role 6) give the SM clock
+  {
+    int slot6 = (kReverse ? 2 : 0);
+    (void)slot6;
+    if (tid == 0) LUCID_TR(args.trace, 6, slot6, 90, (long long)globaltimer_ns());
+  }
   tc_fence_after_sync();
   const uint32_t tmem = s.tmem_base;
 
@@ -587,6 +593,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     if (tid == 0) report_error(ctl, kErrAborted, -1, -1, blockIdx.x, 0);
   }
   tc_fence_before_sync();
+  {
+    int slot6 = (kReverse ? 2 : 0) + 1;
+    (void)slot6;
+    if (tid == 0) LUCID_TR(args.trace, 6, slot6, 91, (long long)globaltimer_ns());
+  }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
