@@ -95,7 +95,10 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines]
+        # samples taken while the timed region ran; a region shorter than the sampling period falls back to
+        # the samples around it (which include idle moments and read high)
+        rows = ([l for (t, l) in self.lines if t0 + 0.02 <= t <= t1] or
+                [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines])
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for l in rows:
@@ -250,6 +253,20 @@ def main():
     t_wall1 = time.time()
     clocks = sampler.stop(t_wall0, t_wall1)
     ms_total = ev0.elapsed_time(ev1)
+    # The SM clock as the kernels see it: one instrumented forward straight after the timed region (GPU
+    # still at its loaded power state) records wall time and SM cycles per row-block; nvidia-smi's
+    # instantaneous readings at 100 ms intervals catch idle moments of a sub-second region and read high.
+    try:
+        _, ts = _forward_sub_fwd(sets[0][0], sets[0][1], use_diag_solve=True, instrument=True)
+        torch.cuda.synchronize()
+        ts = ts.reshape(-1, 8).cpu()
+        ns = (ts[:, 2] - ts[:, 0]).double()
+        keep = ns > 100e3
+        if int(keep.sum()) > 0:
+            clocks["sm_mhz_in_kernel"] = float((ts[:, 6].double()[keep] / ns[keep]).median() * 1e3)
+    except Exception as exc:      # reporting only; never fails the benchmark
+        clocks["sm_mhz_in_kernel"] = None
+        clocks["sm_mhz_in_kernel_error"] = str(exc)[:80]
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -340,6 +357,10 @@ def main():
         roofline = dict(bound="tensor", kernel="dk_kernel", achieved=dk_tflops, peak=peak, unit="TFLOP/s",
                         frac=dk_tflops / peak, traffic=traffic, peak_source=peaks["source"] + " (sustained)",
                         per_kernel_ms=k_ms,
+                        # The kernel forms W for every ORDERED pair of row-blocks (S, G and W*K per tile:
+                        # 6 g per unordered pair, against the 3 g the algorithmic count allows), so the
+                        # tensor pipe executes about twice `achieved`.
+                        executed_tflops=((N // 128) * (N // 128 + 1)) * 3 * G * n_local / (k_ms["bwd_dk"] * 1e-3) / 1e12,
                         per_kernel_tflops=dict(
                             fwd_solve=f_fwd * n_local / nsys / (k_ms["fwd_solve"] * 1e-3) / 1e12,
                             bwd_solve=f_rev * n_local / nsys / (k_ms["bwd_solve"] * 1e-3) / 1e12,

@@ -554,12 +554,15 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         mbar_arrive(&s.stage_full);
         if (tid == 128) {
           if (!wait_barrier(&s.stage_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_STAGE_FULL)) break;
+          LUCID_TR(args.trace, 3, trc, 47, i);
           tma_store_4d(&tm_st, s.rhs, 0, i * kBlock, h, b);
           tma_store_4d(&tm_st, s.rhs + kHalfBytes, 64, i * kBlock, h, b);
           tma_store_commit();
           tma_store_wait_read();
+          LUCID_TR(args.trace, 3, trc, 48, i);
           mbar_arrive(&s.r_free);          // the next row-block's right-hand side may be loaded
           tma_store_wait_all();
+          LUCID_TR(args.trace, 3, trc, 49, i);
           fence_proxy_async_all();
           st_release_gpu(args.flags + chain * T + i, kFlagComplete);
         }
