@@ -11,6 +11,16 @@
 // scaling exp(-|k_r|^2), stores Y_i and publishes it by raising flag[chain][i] with release semantics (one
 // increment per storing warp).  Consumers acquire the complete flag before their TMA load of Y_i.
 //
+// Critical path.  A chain advances one row-block per "publish -> flag -> load -> finish -> publish"
+// round, so everything that does not need the newest predecessor Y_l (l = i-1 forward, i+1 reverse) is
+// taken off that round.  With P_l = exp(K_i K_l^T) and A = X_i (forward, rows of the right-hand side
+// scaled by lam) or X_i^T (reverse, result rows scaled by lam),
+//     Y_i = A (Y_in_i - sum_{j != l} P_j Y_j) - (A P_l) Y_l  =  z - Q Y_l,
+// and both z and Q = A P_l are formed while Y_l is still being computed by another CTA: P_l goes to
+// shared memory (into the K_i buffer, which the S products no longer need) as the right-hand side of one
+// more diagonal product, Q comes back through the idle S buffer, is negated, rounded to 16 bits and parked
+// in the idle P buffer.  Once Y_l has arrived a single product OUT += (-Q) Y_l finishes the row-block.
+//
 // Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 issues the
 // S products and owns TMEM, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warp 3 issues the
 // P*Y and diagonal products, warps 4-7 / 8-11 two exp groups that alternate over the S buffers and share
@@ -31,7 +41,7 @@ struct SolveSmem {
   uint64_t k_empty[4], v_full[4], v_empty[4];
   uint64_t ki_full, ki_free, x_full, vi_full, xr_free, r_free, stage_full;
   uint64_t s_full[2], s_free[2], p_full[2], p_free[2];
-  uint64_t acc_full, acc_free, rhs_full, out_full;
+  uint64_t acc_full, acc_free, rhs_full, out_full, pq_full, q_full;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
   uint32_t tmem_base;
@@ -41,7 +51,7 @@ struct SolveSmem {
 enum SolveBar : int {
   BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
   BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
-  BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL
+  BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL, BAR_PQ_FULL, BAR_Q_FULL
 };
 
 constexpr int kSolveThreads = 384;
@@ -96,6 +106,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     mbar_init(&s.acc_free, 256);
     mbar_init(&s.rhs_full, 256);
     mbar_init(&s.out_full, 1);
+    mbar_init(&s.pq_full, 128);
+    mbar_init(&s.q_full, 1);
     s.abort_flag = 0;
     mbar_fence_init();
   }
@@ -132,6 +144,9 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     return true;
   };
   auto tile_j = [&](int jfirst, int q) -> int { return kReverse ? jfirst - q : jfirst + q; };
+  // Items with a diagonal inverse and at least one predecessor finish through Q (see the file header):
+  // their last tile is not accumulated but folded into OUT after the diagonal product.
+  auto q_route = [&](int n) -> bool { return P.use_diag && n > 0; };
 
   // Each role sets its register budget inside its own branch, so that the compiler ties the budget to
   // the code that runs under it (warps 0-3 form one warpgroup and all execute the same decrease).
@@ -311,9 +326,12 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         }
         if (!alive) break;
         g += n;
-        // every S product of this item has been issued: K_i may be replaced once they complete
-        if (n > 0) umma_commit_w(&s.ki_free);
-        else mbar_arrive_w(&s.ki_free);
+        // every S product of this item has been issued: K_i may be replaced once they complete, unless
+        // the buffer goes on to hold P_l for the Q product (then the P*Y issuer releases it)
+        if (!q_route(n)) {
+          if (n > 0) umma_commit_w(&s.ki_free);
+          else mbar_arrive_w(&s.ki_free);
+        }
       }
     }
   } else if (warp == 3) {
@@ -328,8 +346,10 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       const uint64_t d_x = kReverse ? umma_smem_desc(smem_u32(s.x), kHalfBytes, 1024)
                                     : umma_smem_desc(smem_u32(s.x), 16, 1024);
       const uint64_t d_rhs = umma_smem_desc(smem_u32(s.rhs), kHalfBytes, 1024);
+      const uint64_t d_pl = umma_smem_desc(smem_u32(s.ki), kHalfBytes, 1024);      // P_l, laid out like rhs
       const uint64_t d_vr0 = umma_smem_desc(smem_u32(s.vring[0]), 8192, 1024);
       uint32_t g = 0;
+      uint32_t nq = 0;           // items finished through Q so far (phase of pq_full / q_full)
       bool alive = true;
       int trc = 0;
       (void)trc;
@@ -341,45 +361,58 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
         mbar_arrive_w(&s.tk_empty[slot]);
         int chain, i, n, jfirst;
         if (!item_geometry(ticket, chain, i, n, jfirst)) break;
-        for (int q = 0; q < n; ++q) {
-          const uint32_t gq = g + q;
+        const bool via_q = q_route(n);
+        const int n_acc = via_q ? n - 1 : n;      // tiles accumulated before the diagonal product
+        // ACC (or OUT, with fold) += P[buf] * Y ring tile of tile gq
+        auto issue_py = [&](uint32_t gq, bool first, bool fold) -> bool {
           const uint32_t buf = gq & 1;
-          if (!wait_barrier(&s.p_full[buf], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) {
-            alive = false;
-            break;
-          }
+          if (!wait_barrier(&s.p_full[buf], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) return false;
           if (leader) LUCID_TR(args.trace, 5, trc, 32, gq);
-          if (q == 0 &&
-              !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FREE)) {
-            alive = false;
-            break;
-          }
+          if (first && !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FREE))
+            return false;
           const uint32_t p_tmem = tmem + kTmemP + buf * 64;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             const uint32_t u = gq * 2 + half;
             const uint32_t st = u & 3;
-            if (!wait_barrier(&s.v_full[st], (u >> 2) & 1, cta_abort, ctl, limit, chain, i, BAR_V_FULL)) {
-              alive = false;
-              break;
-            }
+            if (!wait_barrier(&s.v_full[st], (u >> 2) & 1, cta_abort, ctl, limit, chain, i, BAR_V_FULL)) return false;
             tc_fence_after_sync();
             if (leader) LUCID_TR(args.trace, 5, trc, 33, u);
             const uint64_t db = d_vr0 + st * (kHalfBytes >> 4);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
               umma_ts_w(tmem + kTmemAcc, p_tmem + (half * 4 + kk) * 8, db + kk * (2048 >> 4), idesc_pv,
-                        (q | half | kk) ? 1u : 0u);
+                        (!first || fold || half || kk) ? 1u : 0u);
             }
             umma_commit_w(&s.v_empty[st]);
           }
-          if (!alive) break;
           umma_commit_w(&s.p_free[buf]);
           if (leader) LUCID_TR(args.trace, 5, trc, 34, gq);
+          return true;
+        };
+        for (int q = 0; q < n_acc; ++q) {
+          if (!issue_py(g + q, q == 0, false)) {
+            alive = false;
+            break;
+          }
         }
         if (!alive) break;
-        g += n;
         umma_commit_w(&s.acc_full);
+        if (via_q) {
+          // Q = X(^T) P_l into the S buffer the last tile came from (its group has drained it)
+          if (!wait_barrier(&s.pq_full, nq & 1, cta_abort, ctl, limit, chain, i, BAR_PQ_FULL)) break;
+          if (!wait_barrier(&s.x_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_X_FULL)) break;
+          tc_fence_after_sync();
+          const uint32_t q_tmem = tmem + kTmemS + ((g + n - 1) & 1) * 128;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint64_t da = kReverse ? desc_advance(d_x, k * 2048)
+                                         : desc_advance(d_x, (k >> 2) * kHalfBytes + (k & 3) * 32);
+            umma_ss_w(q_tmem, da, desc_advance(d_pl, k * 2048), idesc_out, k ? 1u : 0u);
+          }
+          umma_commit_w(&s.q_full);
+          umma_commit_w(&s.ki_free);
+        }
         // diagonal step
         if (!wait_barrier(&s.rhs_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_RHS_FULL)) break;
         tc_fence_after_sync();
@@ -392,13 +425,19 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
                                          : desc_advance(d_x, (k >> 2) * kHalfBytes + (k & 3) * 32);
             umma_ss_w(tmem + kTmemOut, da, desc_advance(d_rhs, k * 2048), idesc_out, k ? 1u : 0u);
           }
-          umma_commit_w(&s.out_full);
           umma_commit_w(&s.xr_free);
           if (leader) LUCID_TR(args.trace, 5, trc, 37, 0);
+          if (via_q) {
+            // OUT += (-Q) Y_l: the only product that waits for the newest predecessor
+            if (!issue_py(g + n - 1, false, true)) break;
+            ++nq;
+          }
+          umma_commit_w(&s.out_full);
         } else {
           mbar_arrive_w(&s.xr_free);
           mbar_arrive_w(&s.r_free);
         }
+        g += n;
       }
     }
   } else if (warp >= 4) {
@@ -408,6 +447,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
     const int row = ((warp & 3) << 5) + lane;        // TMEM lane == row of the block
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     uint32_t g = 0;
+    uint32_t nq = 0;             // items finished through Q so far (phase of pq_full / q_full)
     bool alive = true;
     int trc = 0;
     (void)trc;
@@ -422,6 +462,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       int chain, i, n, jfirst;
       if (!item_geometry(ticket, chain, i, n, jfirst)) break;
       const int b = chain / H, h = chain % H;
+      const bool via_q = q_route(n);
       long long t_start = 0, c_start = 0;
       if (P.instrument && tid == 128) {
         t_start = (long long)globaltimer_ns();
@@ -450,6 +491,61 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
           tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
           tmem_wait_ld();
         }
+        const uint32_t p_tmem = lane_base + kTmemP + wg * 64;
+        if (via_q && q == n - 1) {
+          // ---- last tile of a Q-route item: P_l to shared memory, Q back through this S buffer ----
+          // P_l (forward: rows scaled by lam, folded into the exponent) in the layout of the rhs buffer,
+          // written over K_i: s_full of the last tile implies that every S product has completed.
+          const float shift = (P.use_diag && !kReverse) ? __log2f(lam) : 0.0f;
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float e0 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + 2 * e]), kLog2e, shift));
+              const float e1 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + 2 * e + 1]), kLog2e, shift));
+              o[e] = pack2_fast<kBf16>(e0, e1);
+            }
+            *reinterpret_cast<uint4*>(s.ki + (c >> 3) * kHalfBytes + sw128_off(row, c & 7)) =
+                make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
+          mbar_arrive(&s.pq_full);
+          if (!wait_barrier(&s.q_full, nq & 1, cta_abort, ctl, limit, chain, i, BAR_Q_FULL)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
+          {
+            const uint32_t s_tmem = lane_base + kTmemS + wg * 128;
+            tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
+            tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
+            tmem_wait_ld();
+          }
+          tc_fence_before_sync();
+          mbar_arrive(&s.s_free[wg]);       // only now may the next tile of this parity overwrite the buffer
+          if (!wait_barrier(&s.p_free[wg], ph ^ 1, cta_abort, ctl, limit, chain, i, BAR_P_FREE)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              pk[e] = pack2<kBf16>(-__uint_as_float(v[c * 32 + 2 * e]), -__uint_as_float(v[c * 32 + 2 * e + 1]));
+            tmem_st16(p_tmem + c * 16, pk);
+          }
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(&s.p_full[wg]);       // -Q is in place for the closing product
+          if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
+          continue;
+        }
         tc_fence_before_sync();
         mbar_arrive(&s.s_free[wg]);
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 46, gq);
@@ -459,7 +555,6 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
           break;
         }
         tc_fence_after_sync();
-        const uint32_t p_tmem = lane_base + kTmemP + wg * 64;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
@@ -473,6 +568,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
       }
       if (!alive) break;
       g += n;
+      if (via_q) ++nq;
 
       // ---- epilogue: this group owns output columns 64*wg .. 64*wg+63 ----
       // Everything that does not depend on the accumulator is done before waiting for it: this
@@ -490,7 +586,7 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
                         wg * 64;
       uint32_t acc[64];
       if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FULL)) break;
-      if (n > 0) {
+      if ((via_q ? n - 1 : n) > 0) {      // tiles accumulated before the diagonal product
         tc_fence_after_sync();
         tmem_ld32(lane_base + kTmemAcc + wg * 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
         tmem_ld32(lane_base + kTmemAcc + wg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
