@@ -81,10 +81,14 @@ static int bshd_map(CUtensorMap* m, bool bf16, const void* p, const int64_t st[3
 
 static int auto_group(int C, int N, int requested) {
   if (requested > 0) return requested < C ? requested : C;
-  // K and Y of one chain take N * 512 bytes; keep a group's working set near the 126 MB L2, and make the
-  // groups equal in size
+  // K and Y of one chain take N * 512 bytes.  Long chains (T >= 256) are throughput-bound and run best with a
+  // group's working set at about half of the 126 MB L2 (measured on B200, forward, ms for groups of
+  // 2/4/8/16 at B*H=16, N=32768: 6.2/4.6/5.0/5.6; 1/2 at B*H=8, N=131072: 38.7/40.4; 2/4/8 at B*H=8, N=65536:
+  // 9.4/10.0/10.9); short chains are bound by the chain latency, which every group pays once, so they take
+  // the whole L2 (4/8/16 at B*H=16, N=16384: 2.4/1.8/1.5).  The groups are made equal in size.
   const long long per_chain = (long long)N * 512;
-  long long gmax = (144ll << 20) / per_chain;
+  const long long budget = (N / kBlock >= 256) ? (72ll << 20) : (144ll << 20);
+  long long gmax = budget / per_chain;
   if (gmax < 1) gmax = 1;
   if (gmax >= C) return C;
   const long long ng = (C + gmax - 1) / gmax;
