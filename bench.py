@@ -259,14 +259,21 @@ def main():
     try:
         _, ts = _forward_sub_fwd(sets[0][0], sets[0][1], use_diag_solve=True, instrument=True)
         torch.cuda.synchronize()
-        ts = ts.reshape(-1, 8).cpu()
-        ns = (ts[:, 2] - ts[:, 0]).double()
+        ts3 = ts.cpu().double()                      # (systems, T, 8): start, loop end, published, flag wait ns, ...
+        ts = ts3.reshape(-1, 8)
+        ns = ts[:, 2] - ts[:, 0]
         keep = ns > 100e3
         if int(keep.sum()) > 0:
-            clocks["sm_mhz_in_kernel"] = float((ts[:, 6].double()[keep] / ns[keep]).median() * 1e3)
+            clocks["sm_mhz_in_kernel"] = float((ts[:, 6][keep] / ns[keep]).median() * 1e3)
+        # The wavefront as measured: time between the publications of consecutive row-blocks of a chain
+        # (its critical path is T such steps per solve) and the share of CTA time spent waiting for flags.
+        pub = ts3[:, :, 2]
+        step_ns = float((pub[:, 1:] - pub[:, :-1]).median()) if pub.shape[1] > 1 else 0.0
+        wavefront = dict(chain_step_ns=step_ns, flag_wait_frac=float(ts[:, 3].sum() / ns.sum()))
     except Exception as exc:      # reporting only; never fails the benchmark
         clocks["sm_mhz_in_kernel"] = None
         clocks["sm_mhz_in_kernel_error"] = str(exc)[:80]
+        wavefront = None
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -365,6 +372,14 @@ def main():
                             fwd_solve=f_fwd * n_local / nsys / (k_ms["fwd_solve"] * 1e-3) / 1e12,
                             bwd_solve=f_rev * n_local / nsys / (k_ms["bwd_solve"] * 1e-3) / 1e12,
                             bwd_dk=dk_tflops))
+        # Bounds asked for by the metric: the tensor roofline of the algorithmic flops on this many GPUs and
+        # the critical path of the two solves (2 * T chain steps at the step time of an unloaded chain, 3.3 us
+        # measured on B200 with one chain per GPU); the fraction is taken against the tighter (larger) one.
+        if wavefront is not None:
+            tensor_ms = total_flops / (world * peaks["bf16_tflops"] * 1e12) * 1e3
+            crit_ms = 2 * (N // 128) * 3.3e-3
+            wavefront.update(tensor_bound_ms=tensor_ms, critical_path_bound_ms=crit_ms,
+                             frac_of_tighter_bound=max(tensor_ms, crit_ms) / ms_step)
         line = dict(metric=METRIC, value=total_flops / (ms_step * 1e-3) / 1e12, unit=UNIT, n_gpus=world,
                     steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True,
                     scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
@@ -374,7 +389,7 @@ def main():
                                 l2="inputs (3 x 128 MiB per step at N=32768) exceed the 126 MB L2; no flush",
                                 seed=0),
                     frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (world * peaks["bf16_tflops"]),
-                    roofline=roofline, clocks=clocks, gpu_launches=4 * args.steps, e2e=e2e)
+                    roofline=roofline, wavefront=wavefront, clocks=clocks, gpu_launches=4 * args.steps, e2e=e2e)
         if not args.no_cpu_baseline and world == 1:
             cb, _ = cpu_naive_sample()
             line["cpu_baseline"] = cb
