@@ -361,17 +361,30 @@ def main():
         # DRAM bytes per dk_kernel launch: 254.9 MB measured by ncu at N=16384 with 16 systems (profiles/), equal to the
         # compulsory bytes (read K, V', dV; write dK), which scale with N and with the systems on this rank
         traffic = 254.9e6 * (N / 16384.0) * (n_local / 16.0)
-        roofline = dict(bound="tensor", kernel="dk_kernel", achieved=dk_tflops, peak=peak, unit="TFLOP/s",
+        T_ = N // 128
+        dk_exec = (T_ * (T_ + 1)) * 3 * G * n_local       # S, G and W*K for every ORDERED pair of row-blocks
+        fused = k_ms["bwd_dk"] < 0.05 * k_ms["bwd_solve"]
+        if fused:
+            # one or two systems per GPU: the library ran the reverse solve and dK in ONE launch (timed here
+            # as bwd_solve); the dominant kernel is then that launch, with the flops of both programs
+            dom_kernel = "bwd_fused_kernel (reverse solve + dK in one launch)"
+            t_dom = (k_ms["bwd_solve"] + k_ms["bwd_dk"]) * 1e-3
+            f_dom = (f_dk + f_rev) * n_local / nsys
+            exec_dom = dk_exec + f_rev * n_local / nsys
+        else:
+            dom_kernel, t_dom, f_dom, exec_dom = "dk_kernel", k_ms["bwd_dk"] * 1e-3, f_dk_local, dk_exec
+        dk_tflops = f_dom / t_dom / 1e12
+        roofline = dict(bound="tensor", kernel=dom_kernel, achieved=dk_tflops, peak=peak, unit="TFLOP/s",
                         frac=dk_tflops / peak, traffic=traffic, peak_source=peaks["source"] + " (sustained)",
                         per_kernel_ms=k_ms,
-                        # The kernel forms W for every ORDERED pair of row-blocks (S, G and W*K per tile:
-                        # 6 g per unordered pair, against the 3 g the algorithmic count allows), so the
-                        # tensor pipe executes about twice `achieved`.
-                        executed_tflops=((N // 128) * (N // 128 + 1)) * 3 * G * n_local / (k_ms["bwd_dk"] * 1e-3) / 1e12,
+                        # The dK program forms W for every ordered pair (6 g per unordered pair, against the 3 g
+                        # the algorithmic count allows), so the tensor pipe executes about twice `achieved`.
+                        executed_tflops=exec_dom / t_dom / 1e12,
                         per_kernel_tflops=dict(
                             fwd_solve=f_fwd * n_local / nsys / (k_ms["fwd_solve"] * 1e-3) / 1e12,
-                            bwd_solve=f_rev * n_local / nsys / (k_ms["bwd_solve"] * 1e-3) / 1e12,
-                            bwd_dk=dk_tflops))
+                            bwd_solve=None if fused else f_rev * n_local / nsys / (k_ms["bwd_solve"] * 1e-3) / 1e12,
+                            bwd_dk=None if fused else dk_tflops,
+                            bwd_fused=dk_tflops if fused else None))
         # Bounds asked for by the metric: the tensor roofline of the algorithmic flops on this many GPUs and
         # the critical path of the two solves (2 * T chain steps at the step time of an unloaded chain, 3.3 us
         # measured on B200 with one chain per GPU); the fraction is taken against the tighter (larger) one.
@@ -389,7 +402,7 @@ def main():
                                 l2="inputs (3 x 128 MiB per step at N=32768) exceed the 126 MB L2; no flush",
                                 seed=0),
                     frac_of_bf16_peak=total_flops / (ms_step * 1e-3) / 1e12 / (world * peaks["bf16_tflops"]),
-                    roofline=roofline, wavefront=wavefront, clocks=clocks, gpu_launches=4 * args.steps, e2e=e2e)
+                    roofline=roofline, wavefront=wavefront, clocks=clocks, gpu_launches=(3 if fused else 4) * args.steps, e2e=e2e)
         if not args.no_cpu_baseline and world == 1:
             cb, _ = cpu_naive_sample()
             line["cpu_baseline"] = cb

@@ -128,6 +128,13 @@ void lucid_set_wait_limit_ns(uint64_t ns);
  * whose grid is one CTA per row-block in launch order (tile_scheduler.py:105-117). */
 void lucid_set_head_steps(int steps);
 
+/* Combined backward (mode LUCID_BWD_COMBINED): with at most `max_chains` (batch, head) systems the reverse
+ * solve, then bound by its chain latency, and the dK program run in ONE launch - `solve_ctas` CTAs solve,
+ * the others compute dK row-blocks as the solve publishes them and are joined by the solving CTAs at the
+ * end (0 = automatic share, 47 %).  Default max_chains = 2; 0 disables the fusion.  The reference's BackwardSubSm90 likewise runs its two phases in one
+ * launch (forward_sub_bwd.py:1053-1269). */
+void lucid_set_fused_backward(int max_chains, int solve_ctas);
+
 /* Per-kernel timing for benchmarks: the NEXT lucid_fwd_sub / lucid_bwd_sub call records these
  * cudaEvent_t handles on its stream (before the diagonal-prep kernel, after it, after the solve kernel,
  * after the dK kernel); any of them may be NULL.  The handles are forgotten after that call.  Stands in

@@ -28,7 +28,8 @@ _I64x3 = ctypes.c_int64 * 3
 
 EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_read_status",
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
-           "lucid_profile_next_call", "lucid_set_head_steps", "lucid_fwd_sub_static")
+           "lucid_profile_next_call", "lucid_set_head_steps", "lucid_fwd_sub_static",
+           "lucid_set_fused_backward")
 
 
 class LucidKernelError(RuntimeError):
@@ -76,6 +77,13 @@ def load() -> ctypes.CDLL:
         lib.lucid_status_string.argtypes = [c.c_int]
         lib.lucid_set_head_steps.restype = None
         lib.lucid_set_head_steps.argtypes = [c.c_int]
+        lib.lucid_set_fused_backward.restype = None
+        lib.lucid_set_fused_backward.argtypes = [c.c_int, c.c_int]
+        # LUCID_B200_FUSED_BWD="max_chains[,solve_ctas]" overrides the library's default (4, automatic)
+        env = os.environ.get("LUCID_B200_FUSED_BWD")
+        if env:
+            parts = [int(x) for x in env.split(",")]
+            lib.lucid_set_fused_backward(parts[0], parts[1] if len(parts) > 1 else 0)
         lib.lucid_profile_next_call.restype = None
         lib.lucid_profile_next_call.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p]
         lib.lucid_set_wait_limit_ns.restype = None

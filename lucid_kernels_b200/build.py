@@ -16,7 +16,9 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "_lucid_b200.so")
-SOURCES = ["api.cu", "solve.cu", "diag_prep.cu", "dk.cu"]
+SOURCES = ["api.cu", "solve.cu", "diag_prep.cu", "dk.cu", "bwd_fused.cu"]
+# sources that textually include other sources
+INCLUDES = {"bwd_fused.cu": ["solve.cu", "dk.cu"]}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 
@@ -42,7 +44,9 @@ def build(verbose: bool = False, force: bool = False) -> str:
     for src in SOURCES:
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJ, src[:-3] + ".o")
-        if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr_time):
+        dep_time = max([os.path.getmtime(s), hdr_time] +
+                       [os.path.getmtime(os.path.join(CSRC, d)) for d in INCLUDES.get(src, [])])
+        if force or not os.path.exists(o) or os.path.getmtime(o) < dep_time:
             jobs.append((s, o))
 
     def compile_one(job):

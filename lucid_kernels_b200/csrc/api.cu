@@ -12,6 +12,8 @@ static unsigned long long g_wait_ns = 2000000000ull;
 // optional per-kernel timing: events recorded around the kernels of the NEXT call, then forgotten
 static cudaEvent_t g_events[4] = {nullptr, nullptr, nullptr, nullptr};
 static long long* g_trace = nullptr;
+static int g_fuse_max_chains = 2;   // combined backward: fuse solve and dK into one launch up to this many chains
+static int g_fuse_solve_ctas = 0;   // 0 = automatic share
 static int g_head = -1;   // scheduler knob; < 0 = default
 static inline void record_event(int i, cudaStream_t stream) {
   if (g_events[i]) cudaEventRecord(g_events[i], stream);
@@ -118,10 +120,17 @@ static Problem make_problem(int B, int N, int H, int flags, int window, int grou
   return p;
 }
 
-// shared by forward and backward: prep (if diag) + one solve
+// What the combined backward hands to run_solve when the dK program is to run in the solve's launch.
+struct FusedDk {
+  CUtensorMap tm_vp, tm_dv;
+  DkArgs args;
+  int n_solve;
+};
+
+// shared by forward and backward: prep (if diag) + one solve (+ the dK program in the same launch)
 static int run_solve(bool reverse, const void* k, const void* in, void* out, const int64_t ks[3],
                      const int64_t ins[3], const int64_t outs[3], const Problem& p, bool bf16, uint8_t* ws,
-                     const Layout& lay, cudaStream_t stream) {
+                     const Layout& lay, cudaStream_t stream, FusedDk* fused = nullptr) {
   const int CT = p.C * p.T;
   Control* ctl = reinterpret_cast<Control*>(ws);
   CUtensorMap tm_k, tm_in, tm_out, tm_x, tm_st;
@@ -160,7 +169,15 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
   const int sms = sm_count();
   if (sms <= 0) return LUCID_E_NO_DEVICE;
   const int grid = CT < sms ? CT : sms;
-  if ((e = launch_solve(bf16, reverse, tm_k, tm_in, tm_out, tm_x, tm_st, sa, grid, stream)) != cudaSuccess) return (int)e;
+  if (fused) {
+    fused->args.follow_flags = sa.flags;
+    fused->args.follow_ctl = sa.ctl;
+    e = launch_bwd_fused(bf16, tm_k, tm_in, tm_out, tm_x, tm_st, fused->tm_vp, fused->tm_dv, sa, fused->args,
+                         fused->n_solve, sms, stream);
+  } else {
+    e = launch_solve(bf16, reverse, tm_k, tm_in, tm_out, tm_x, tm_st, sa, grid, stream);
+  }
+  if (e != cudaSuccess) return (int)e;
   record_event(2, stream);
   return 0;
 }
@@ -184,6 +201,11 @@ size_t lucid_workspace_timestamps_offset(int B, int N, int H) {
 void lucid_set_wait_limit_ns(uint64_t ns) { g_wait_ns = ns; }
 
 void lucid_set_head_steps(int steps) { g_head = steps; }
+
+void lucid_set_fused_backward(int max_chains, int solve_ctas) {
+  g_fuse_max_chains = max_chains;
+  g_fuse_solve_ctas = solve_ctas;
+}
 
 #ifdef LUCID_TRACE
 void lucid_debug_set_trace(void* buf) { g_trace = static_cast<long long*>(buf); }
@@ -282,26 +304,44 @@ int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void
   if (e != cudaSuccess) return (int)e;
   const bool bf16 = dtype == LUCID_DTYPE_BF16;
   const Problem p = make_problem(B, N, H, flags, 0, chain_group);
-  rc = run_solve(true, k, dv_prime, dv, k_strides, dvp_strides, dv_strides, p, bf16, ws, lay, stream);
+  const int sms = sm_count();
+  if (sms <= 0) return LUCID_E_NO_DEVICE;
+  const int CT = p.C * p.T;
+  FusedDk fd;
+  CUtensorMap tm_k;
+  if (mode == LUCID_BWD_COMBINED) {
+    if ((rc = bshd_map(&tm_k, bf16, k, k_strides, B, N, H, 128))) return rc;
+    if ((rc = bshd_map(&fd.tm_vp, bf16, v_prime, vp_strides, B, N, H, 128))) return rc;
+    if ((rc = bshd_map(&fd.tm_dv, bf16, dv, dv_strides, B, N, H, 128))) return rc;
+    fd.args.dk = dk;
+    fd.args.dk_strides = Strides{dk_strides[0], dk_strides[1], dk_strides[2]};
+    fd.args.ctl = reinterpret_cast<Control*>(ws) + 2;
+    fd.args.follow_flags = nullptr;
+    fd.args.follow_ctl = nullptr;
+    fd.args.trace = g_trace;
+    fd.args.p = p;
+  }
+  // With one or two chains the reverse solve is bound by its chain latency and leaves SMs idle: the dK
+  // program then runs in the same launch on the other CTAs, and the solve's CTAs join it when the solve's
+  // row-blocks have all been taken.  Measured on B200 (backward, ms, separate launches against one launch
+  // with 45 / 56 / 64 / 72 / 90 solve CTAs): 2 chains of N=32768: 2.14 against 2.24 / 1.98 / 1.88 / 1.87 /
+  // 1.95; 1 chain: 1.75 against 1.60 / 1.50 / 1.50 / 1.49 / 1.49; 4 chains: 3.62 against 4.27 / 3.80 / 3.73 /
+  // 3.78 / 3.78 (no gain, hence the limit of 2).  Needs at least two row-blocks per SM.
+  int n_solve = g_fuse_solve_ctas > 0 ? g_fuse_solve_ctas : (sms * 47 + 50) / 100;
+  if (n_solve >= sms) n_solve = sms - 1;
+  const bool fuse = mode == LUCID_BWD_COMBINED && p.C <= g_fuse_max_chains && !p.instrument && !p.no_sync &&
+                    CT >= 2 * sms && n_solve >= 1;
+  fd.n_solve = n_solve;
+  rc = run_solve(true, k, dv_prime, dv, k_strides, dvp_strides, dv_strides, p, bf16, ws, lay, stream,
+                 fuse ? &fd : nullptr);
   cudaEvent_t ev_dk = g_events[3];
   memset(g_events, 0, sizeof(g_events));
   if (rc) return rc;
   if (mode == LUCID_BWD_COMBINED) {
-    CUtensorMap tm_k, tm_vp, tm_dv;
-    if ((rc = bshd_map(&tm_k, bf16, k, k_strides, B, N, H, 128))) return rc;
-    if ((rc = bshd_map(&tm_vp, bf16, v_prime, vp_strides, B, N, H, 128))) return rc;
-    if ((rc = bshd_map(&tm_dv, bf16, dv, dv_strides, B, N, H, 128))) return rc;
-    DkArgs da;
-    da.dk = dk;
-    da.dk_strides = Strides{dk_strides[0], dk_strides[1], dk_strides[2]};
-    da.ctl = reinterpret_cast<Control*>(ws) + 2;
-    da.trace = g_trace;
-    da.p = p;
-    const int sms = sm_count();
-    if (sms <= 0) return LUCID_E_NO_DEVICE;
-    const int CT = p.C * p.T;
-    const int grid = CT < sms ? CT : sms;
-    if ((e = launch_dk(bf16, tm_k, tm_vp, tm_dv, da, grid, stream)) != cudaSuccess) return (int)e;
+    if (!fuse) {
+      const int grid = CT < sms ? CT : sms;
+      if ((e = launch_dk(bf16, tm_k, fd.tm_vp, fd.tm_dv, fd.args, grid, stream)) != cudaSuccess) return (int)e;
+    }
     if (ev_dk) cudaEventRecord(ev_dk, stream);
   }
   return 0;

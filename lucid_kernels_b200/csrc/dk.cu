@@ -50,12 +50,16 @@ enum DkBar : int {
 constexpr int kDkThreads = 384;
 constexpr int kDkS0 = 0, kDkS1 = 128, kDkG = 256, kDkAcc = 384;
 
+// The whole CTA program, callable from more than one kernel (the tensor maps must be __grid_constant__
+// parameters of the calling kernel).  With args.follow_flags set, the CTA runs beside the reverse solve in
+// the same launch: row-blocks are taken from the last one downwards, step-major over the chains, and each
+// waits (bounded) for the flag with which the solve publishes dV_i - dV_j of every later block has then
+// been published as well, and dK_i needs nothing else of the solve.
 template <bool kBf16>
-__global__ void __launch_bounds__(kDkThreads, 1)
-dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
-          const __grid_constant__ CUtensorMap tm_vp,   // V',  box 64 x 128
-          const __grid_constant__ CUtensorMap tm_dv,   // dV,  box 64 x 128
-          const DkArgs args) {
+__device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 64 x 128
+                                        const CUtensorMap& tm_vp,   // V',  box 64 x 128
+                                        const CUtensorMap& tm_dv,   // dV,  box 64 x 128
+                                        const DkArgs& args) {
   extern __shared__ uint8_t smem_raw[];
   DkSmem& s = *reinterpret_cast<DkSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const Problem& P = args.p;
@@ -111,8 +115,13 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
   //   n_low = i (+1 with D1); tiles q < n_low are "lower" (A = dV_i, Z = V'_j).
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& n_low) -> bool {
     if (ticket >= P.C * T) return false;
-    chain = ticket / T;
-    i = ticket % T;
+    if (args.follow_flags) {
+      chain = ticket % P.C;
+      i = T - 1 - ticket / P.C;
+    } else {
+      chain = ticket / T;
+      i = ticket % T;
+    }
     n_low = i + (diag_tiles ? 1 : 0);
     n = T - 1 + (diag_tiles ? 2 : 0);
     return true;
@@ -144,6 +153,12 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
         mbar_expect_tx(&s.ki_full, kTileBytes);
         tma_load_4d(s.ki, &tm_k, &s.ki_full, 0, i * kBlock, h, b);
         tma_load_4d(s.ki + kHalfBytes, &tm_k, &s.ki_full, 64, i * kBlock, h, b);
+        if (args.follow_flags) {
+          // dV_i (and with it every dV_j, j > i) has been published by the reverse solve of this launch
+          if (!wait_flag(args.follow_flags + chain * T + i, cta_abort, args.follow_ctl, limit, chain, i, i, nullptr))
+            break;
+          fence_proxy_async_all();   // flag acquired in the generic proxy; dV is read by TMA
+        }
         // A buffer: dV_i for the lower tiles (skipped when there are none), V'_i for the upper tiles
         auto load_a = [&](const CUtensorMap* tm) -> bool {
           if (!wait_barrier(&s.ai_free, (swaps & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_AI_FREE)) return false;
@@ -473,6 +488,14 @@ dk_kernel(const __grid_constant__ CUtensorMap tm_k,    // K,   box 64 x 128
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+#ifndef LUCID_BODY_ONLY
+template <bool kBf16>
+__global__ void __launch_bounds__(kDkThreads, 1)
+dk_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_vp,
+          const __grid_constant__ CUtensorMap tm_dv, const DkArgs args) {
+  dk_body<kBf16>(tm_k, tm_vp, tm_dv, args);
+}
+
 size_t dk_smem_bytes() { return sizeof(DkSmem) + 1024; }
 
 cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,
@@ -489,5 +512,6 @@ cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_
   }
   return cudaGetLastError();
 }
+#endif  // LUCID_BODY_ONLY
 
 }  // namespace lucid

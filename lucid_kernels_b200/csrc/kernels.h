@@ -27,7 +27,9 @@ struct DkArgs {
   void* dk;
   Strides dk_strides;
   Control* ctl;
-  long long* trace;       // debugging builds only (LUCID_TRACE); null otherwise
+  const int* follow_flags;  // (C, T) flags of the reverse solve running in the same launch, or null
+  Control* follow_ctl;      // that solve's control block (its failure releases the flag waits)
+  long long* trace;         // debugging builds only (LUCID_TRACE); null otherwise
   Problem p;
 };
 
@@ -38,5 +40,11 @@ cudaError_t launch_diag_prep(bool bf16, const CUtensorMap& tm_k, const PrepArgs&
                              cudaStream_t stream);
 cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,
                       const DkArgs& args, int grid, cudaStream_t stream);
+// Reverse solve (CTAs 0 .. n_solve-1) and dK (the remaining CTAs) in one launch; dargs.follow_flags must
+// point at the solve's flags.  grid must not exceed the number of SMs: the dK CTAs wait for the solve CTAs.
+cudaError_t launch_bwd_fused(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_in, const CUtensorMap& tm_out,
+                             const CUtensorMap& tm_x, const CUtensorMap& tm_st, const CUtensorMap& tm_vp,
+                             const CUtensorMap& tm_dv, const SolveArgs& sargs, const DkArgs& dargs, int n_solve,
+                             int grid, cudaStream_t stream);
 
 }  // namespace lucid

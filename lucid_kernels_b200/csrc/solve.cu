@@ -62,15 +62,18 @@ constexpr int kTmemS = 0, kTmemP = 256, kTmemAcc = 384, kTmemOut = 384;
 // Register budget per thread after the role split: the exp / epilogue groups hold a whole S row (128
 // fp32) in registers, the four service warps need few.  128 * 56 + 256 * 224 = 64512 <= 65536.
 constexpr int kRegsService = 72, kRegsExp = 216;
+constexpr int kRegsLaunch = 168;   // what __launch_bounds__(384, 1) gives every thread at launch
 
+// The whole CTA program, callable from more than one kernel (the tensor maps must be __grid_constant__
+// parameters of the calling kernel).
 template <bool kBf16, bool kReverse>
-__global__ void __launch_bounds__(kSolveThreads, 1)
-solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
-             const __grid_constant__ CUtensorMap tm_in,    // V (or dV'), box 64 x 128
-             const __grid_constant__ CUtensorMap tm_out,   // Y, box 64 x 64
-             const __grid_constant__ CUtensorMap tm_x,     // X workspace (2D), box 64 x 128
-             const __grid_constant__ CUtensorMap tm_st,    // Y again, box 64 x 128, for the TMA store of Y_i
-             const SolveArgs args) {
+__device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, box 64 x 128
+                                           const CUtensorMap& tm_in,    // V (or dV'), box 64 x 128
+                                           const CUtensorMap& tm_out,   // Y, box 64 x 64
+                                           const CUtensorMap& tm_x,     // X workspace (2D), box 64 x 128
+                                           const CUtensorMap& tm_st,    // Y, box 64 x 128, for the TMA store
+                                           const SolveArgs& args,
+                                           const bool last_program = true) {   // no TMEM allocation follows
   extern __shared__ uint8_t smem_raw[];
   SolveSmem& s = *reinterpret_cast<SolveSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const Problem& P = args.p;
@@ -113,7 +116,8 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, 512);
-    tmem_relinquish();
+    // giving up the allocation permit is final for the CTA: only when no other program follows in this kernel
+    if (last_program) tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -699,6 +703,26 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k,     // K, box 64 x 128
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
+  if (!last_program) {
+    // Another CTA program follows in the same kernel: it lays its own barriers over this memory, and its
+    // warps run with the kernel's launch-time register count again (the exp warpgroups give back what the
+    // service warpgroup then takes).
+    if (tid == 0) {
+      for (uint64_t* b = &s.k_full[0]; b < reinterpret_cast<uint64_t*>(&s.tk_slot[0]); ++b) mbar_inval(b);
+    }
+    if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLaunch));
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsLaunch));
+    __syncthreads();
+  }
+}
+
+#ifndef LUCID_BODY_ONLY
+template <bool kBf16, bool kReverse>
+__global__ void __launch_bounds__(kSolveThreads, 1)
+solve_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_in,
+             const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_x,
+             const __grid_constant__ CUtensorMap tm_st, const SolveArgs args) {
+  solve_body<kBf16, kReverse>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -727,5 +751,6 @@ cudaError_t launch_solve(bool bf16, bool reverse, const CUtensorMap& tm_k, const
   return reverse ? launch_solve_t<false, true>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
                  : launch_solve_t<false, false>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream);
 }
+#endif  // LUCID_BODY_ONLY
 
 }  // namespace lucid

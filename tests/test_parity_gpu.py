@@ -169,6 +169,28 @@ def test_large_sizes_by_properties(ops):
     assert orc.rel_err(comb, 0.5 * vp.float() + 2.0 * vp2.float()) < 0.01
 
 
+@pytest.mark.parametrize("dtype,H", [(torch.bfloat16, 2), (torch.float16, 1)])
+def test_backward_in_one_launch_matches_separate_launches(ops, dtype, H):
+    """With one or two systems per GPU the combined backward runs the reverse solve and the dK program in one
+    launch (the dK CTAs follow the solve's flags).  Same arithmetic in the same order: bit-identical."""
+    from lucid_kernels_b200 import _cabi
+
+    lib = _cabi.load()
+    K, V, G = orc.make_inputs(1, 32768, H, dtype=dtype, seed=11)
+    Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+    vp = ops._forward_sub_fwd(Kc, Vc, check=True)
+    try:
+        lib.lucid_set_fused_backward(0, 0)                      # separate launches
+        dv0, dk0 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+        for solve_ctas in (0, 20, 120):                         # automatic share, a small and a large one
+            lib.lucid_set_fused_backward(2, solve_ctas)
+            dv1, dk1 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+            assert torch.equal(dv0, dv1) and torch.equal(dk0, dk1), solve_ctas
+    finally:
+        lib.lucid_set_fused_backward(2, 0)                      # library default
+    assert bool(torch.isfinite(dk0.float()).all())
+
+
 def test_argument_errors(ops):
     K, V, _ = orc.make_inputs(1, 256, 1, dtype=torch.bfloat16)
     with pytest.raises(AssertionError):
