@@ -20,7 +20,7 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_dv, const SolveArgs sargs, const DkArgs dargs,
                  const int n_solve) {
   // A solve CTA joins the dK program once the solve's row-blocks have all been taken.
-  if ((int)blockIdx.x < n_solve) solve_body<kBf16, true>(tm_k, tm_in, tm_out, tm_x, tm_st, sargs, false);
+  if ((int)blockIdx.x < n_solve) solve_body<kBf16, true, 2>(tm_k, tm_in, tm_out, tm_x, tm_st, sargs, false);
   dk_body<kBf16>(tm_k, tm_vp, tm_dv, dargs);
 }
 

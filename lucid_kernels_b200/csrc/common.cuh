@@ -77,9 +77,10 @@ __device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, vol
   return true;
 }
 
-// A row-block is published by eight warps, each adding 1 to its flag with release semantics after its
-// own stores; the block is complete when the flag reaches kFlagComplete.
-constexpr int kFlagComplete = 8;
+// A row-block is complete when its flag reaches kFlagComplete: set at once by the thread that stored the
+// block with TMA, or reached by the storing warps (8 or 16 of them) each adding their share with release
+// semantics after their own plain stores.
+constexpr int kFlagComplete = 16;
 
 // Wait until the flag reaches kFlagComplete (acquire).  Polls the global status word so that one CTA's
 // failure releases every waiter.  Returns the nanoseconds spent waiting through *waited when non-null.

@@ -23,9 +23,15 @@
 //
 // Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 issues the
 // S products and owns TMEM, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warp 3 issues the
-// P*Y and diagonal products, warps 4-7 / 8-11 two exp groups that alternate over the S buffers and share
-// the epilogue (64 columns each).  Two issuing warps because tcgen05.mma issue is nearly synchronous
+// P*Y and diagonal products, warps 4-7 / 8-11 two exp groups that split every tile's columns (64 each)
+// and share the epilogue the same way.  Two issuing warps because tcgen05.mma issue is nearly synchronous
 // with execution (the queue holds only a few instructions): the waits of one overlap the MMAs of the other.
+//
+// TMEM: three S buffers (tile g uses buffer g % 3) and the accumulator.  An exp thread streams its 64
+// columns of S through registers in 16-column chunks (the next chunk's load in flight) and writes the
+// packed P chunk over S columns it has already consumed, so P needs no buffer of its own and the S
+// products run up to three tiles ahead of the P*Y products; a buffer returns to the S issuer when the
+// P*Y product that read it has completed.
 #include <type_traits>
 #include "kernels.h"
 
@@ -40,7 +46,7 @@ struct SolveSmem {
   alignas(8) uint64_t k_full[4];
   uint64_t k_empty[4], v_full[4], v_empty[4];
   uint64_t ki_full, ki_free, x_full, vi_full, xr_free, r_free, stage_full;
-  uint64_t s_full[2], s_free[2], p_full[2], p_free[2];
+  uint64_t s_full[3], sbuf_free[3], p_full[3];
   uint64_t acc_full, acc_free, rhs_full, out_full, pq_full, q_full;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
@@ -54,19 +60,25 @@ enum SolveBar : int {
   BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL, BAR_PQ_FULL, BAR_Q_FULL
 };
 
-constexpr int kSolveThreads = 384;
-// TMEM columns: two S buffers (fp32, 128 columns each), two P buffers (16-bit pairs, 64 columns each)
-// and the accumulator; the diagonal product reuses the accumulator's columns once the epilogue has
-// read them.  Tile g uses S[g & 1] and P[g & 1].
-constexpr int kTmemS = 0, kTmemP = 256, kTmemAcc = 384, kTmemOut = 384;
+// Block size: four service warps plus kG exp groups of four warps (128 threads, one per row).
+constexpr int solve_threads(int groups) { return 128 + 128 * groups; }
+constexpr int kSolveThreads = solve_threads(2);          // the variant that shares a launch with the dK program
+constexpr int kSolveGroups = 4;                          // the stand-alone kernels
+// TMEM columns: three S buffers (fp32, 128 columns each; P is packed over columns 0-31 and 64-95 of the
+// same buffer) and the accumulator; the diagonal product reuses the accumulator's columns once the
+// epilogue has read them.  Tile g uses S[g % 3].
+constexpr int kTmemS = 0, kTmemAcc = 384, kTmemOut = 384;
 // Register budget per thread after the role split: the exp / epilogue groups hold a whole S row (128
 // fp32) in registers, the four service warps need few.  128 * 56 + 256 * 224 = 64512 <= 65536.
-constexpr int kRegsService = 72, kRegsExp = 216;
-constexpr int kRegsLaunch = 168;   // what __launch_bounds__(384, 1) gives every thread at launch
+// Register budgets after the role split (setmaxnreg), for kG = 2: 128 * 72 + 256 * 216 = 64512; for kG = 4
+// (640 threads, 96 registers each at launch): 128 * 64 + 512 * 104 = 61440.
+template <int kG> struct SolveRegs;
+template <> struct SolveRegs<2> { static constexpr int service = 72, exp = 216, launch = 168; };
+template <> struct SolveRegs<4> { static constexpr int service = 64, exp = 104, launch = 96; };
 
 // The whole CTA program, callable from more than one kernel (the tensor maps must be __grid_constant__
 // parameters of the calling kernel).
-template <bool kBf16, bool kReverse>
+template <bool kBf16, bool kReverse, int kG>
 __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, box 64 x 128
                                            const CUtensorMap& tm_in,    // V (or dV'), box 64 x 128
                                            const CUtensorMap& tm_out,   // Y, box 64 x 64
@@ -82,6 +94,10 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
   const int T = P.T, H = P.H;
   const unsigned long long limit = P.wait_ns;
   volatile int* cta_abort = &s.abort_flag;
+  constexpr int kExpThreads = 128 * kG;      // exp / epilogue threads
+  constexpr int kCols = 128 / kG;            // columns of a tile (and of the output) per exp group
+  constexpr int kRegsService = SolveRegs<kG>::service, kRegsExp = SolveRegs<kG>::exp,
+                kRegsLaunch = SolveRegs<kG>::launch;
 
   if (tid == 0) {
     for (int i = 0; i < 4; ++i) {
@@ -96,20 +112,21 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     mbar_init(&s.vi_full, 1);
     mbar_init(&s.xr_free, 1);
     mbar_init(&s.r_free, 1);
-    mbar_init(&s.stage_full, 256);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(&s.stage_full, kExpThreads);
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&s.s_full[i], 1);
-      mbar_init(&s.s_free[i], 128);
-      mbar_init(&s.p_full[i], 128);
-      mbar_init(&s.p_free[i], 1);
+      mbar_init(&s.sbuf_free[i], 1);
+      mbar_init(&s.p_full[i], kExpThreads);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s.tk_full[i], 1);
-      mbar_init(&s.tk_empty[i], 11);
+      mbar_init(&s.tk_empty[i], 3 + 4 * kG);
     }
     mbar_init(&s.acc_full, 1);
-    mbar_init(&s.acc_free, 256);
-    mbar_init(&s.rhs_full, 256);
+    mbar_init(&s.acc_free, kExpThreads);
+    mbar_init(&s.rhs_full, kExpThreads);
     mbar_init(&s.out_full, 1);
-    mbar_init(&s.pq_full, 128);
+    mbar_init(&s.pq_full, kExpThreads);
     mbar_init(&s.q_full, 1);
     s.abort_flag = 0;
     mbar_fence_init();
@@ -132,7 +149,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
 
   // Every role walks the same sequence of items; `it` counts items, `g` counts (i, j) tiles and `u`
   // half-tiles, all per CTA, so that ring stages and barrier phases agree between roles.  Tile g uses
-  // buffers g & 1 in phase (g >> 1) & 1 and is exponentiated by group g & 1.
+  // S buffer g % 3 in phase (g / 3) & 1.
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& jfirst) -> bool {
     int step;
     if (!decode_ticket(ticket, P.C, T, P.group, P.head, chain, step)) return false;
@@ -298,9 +315,9 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         if (leader) LUCID_TR(args.trace, 2, trc, 35, n);
         for (int q = 0; q < n; ++q) {
           const uint32_t gq = g + q;
-          const uint32_t buf = gq & 1;
-          // the exp group has copied this buffer's previous tile (two tiles ago) into registers
-          if (!wait_barrier(&s.s_free[buf], ((gq >> 1) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_S_FREE)) {
+          const uint32_t buf = gq % 3;
+          // the P*Y product of three tiles ago, which read P from this buffer, has completed
+          if (!wait_barrier(&s.sbuf_free[buf], ((gq / 3) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_S_FREE)) {
             alive = false;
             break;
           }
@@ -369,12 +386,12 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         const int n_acc = via_q ? n - 1 : n;      // tiles accumulated before the diagonal product
         // ACC (or OUT, with fold) += P[buf] * Y ring tile of tile gq
         auto issue_py = [&](uint32_t gq, bool first, bool fold) -> bool {
-          const uint32_t buf = gq & 1;
-          if (!wait_barrier(&s.p_full[buf], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) return false;
+          const uint32_t buf = gq % 3;
+          if (!wait_barrier(&s.p_full[buf], (gq / 3) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) return false;
           if (leader) LUCID_TR(args.trace, 5, trc, 32, gq);
           if (first && !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FREE))
             return false;
-          const uint32_t p_tmem = tmem + kTmemP + buf * 64;
+          const uint32_t p_tmem = tmem + kTmemS + buf * 128;   // group g's P: columns g*kCols .. + kCols/2
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             const uint32_t u = gq * 2 + half;
@@ -385,12 +402,15 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
             const uint64_t db = d_vr0 + st * (kHalfBytes >> 4);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              umma_ts_w(tmem + kTmemAcc, p_tmem + (half * 4 + kk) * 8, db + kk * (2048 >> 4), idesc_pv,
+              // k-step ks = 4*half + kk covers K columns 16*ks ..: group ks / (kCols/16), its chunk ks % (kCols/16)
+              umma_ts_w(tmem + kTmemAcc,
+                        p_tmem + ((half * 4 + kk) / (kCols / 16)) * kCols + ((half * 4 + kk) % (kCols / 16)) * 8,
+                        db + kk * (2048 >> 4), idesc_pv,
                         (!first || fold || half || kk) ? 1u : 0u);
             }
             umma_commit_w(&s.v_empty[st]);
           }
-          umma_commit_w(&s.p_free[buf]);
+          umma_commit_w(&s.sbuf_free[buf]);
           if (leader) LUCID_TR(args.trace, 5, trc, 34, gq);
           return true;
         };
@@ -407,7 +427,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           if (!wait_barrier(&s.pq_full, nq & 1, cta_abort, ctl, limit, chain, i, BAR_PQ_FULL)) break;
           if (!wait_barrier(&s.x_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_X_FULL)) break;
           tc_fence_after_sync();
-          const uint32_t q_tmem = tmem + kTmemS + ((g + n - 1) & 1) * 128;
+          const uint32_t q_tmem = tmem + kTmemS + ((g + n - 1) % 3) * 128;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint64_t da = kReverse ? desc_advance(d_x, k * 2048)
@@ -447,7 +467,12 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
   } else if (warp >= 4) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsExp));
     // =========================== exp groups + epilogue ===========================
-    const int wg = (warp - 4) >> 2;                  // 0 or 1: S buffer parity, epilogue column panel
+    const int wg = (warp - 4) >> 2;                  // exp group: columns kCols*wg .. of every tile and of the output
+    constexpr int kCh = kCols / 16;                  // 16-column chunks per thread and tile
+    constexpr int kVec = kCols / 8;                  // 16-byte vectors of 16-bit values per thread and row
+    uint8_t* const my_ki = s.ki + (wg * kCols / 64) * kHalfBytes;     // this group's 64-column panel ...
+    uint8_t* const my_rhs = s.rhs + (wg * kCols / 64) * kHalfBytes;
+    const uint32_t vec0 = (wg * kCols % 64) / 8;                       // ... and its first vector in a panel row
     const int row = ((warp & 3) << 5) + lane;        // TMEM lane == row of the block
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     uint32_t g = 0;
@@ -455,7 +480,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     bool alive = true;
     int trc = 0;
     (void)trc;
-    const bool tr_lead = (tid == 128 || tid == 256);
+    const bool tr_lead = (tid == 128 || tid == 256) && wg < 2;
     (void)tr_lead;
     for (int it = 0; alive; ++it) {
       const int slot = it & 1;
@@ -474,35 +499,30 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
       }
       const float lam = P.use_diag ? args.lam_inv[(chain * T + i) * kBlock + row] : 1.0f;
 
-      // ---- P = exp(S) for the tiles of my parity ----
+      // ---- P = exp(S): this group's kCols columns of every tile ----
       for (int q = 0; q < n; ++q) {
         const uint32_t gq = g + q;
-        if ((gq & 1) != (uint32_t)wg) continue;
-        const uint32_t ph = (gq >> 1) & 1;
-        if (!wait_barrier(&s.s_full[wg], ph, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
+        const uint32_t buf = gq % 3;
+        const uint32_t ph = (gq / 3) & 1;
+        if (!wait_barrier(&s.s_full[buf], ph, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
           alive = false;
           break;
         }
         tc_fence_after_sync();
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 40, gq);
-        // the whole S row goes to registers at once, which frees the S buffer for the tile after next
-        uint32_t v[128];
-        {
-          const uint32_t s_tmem = lane_base + kTmemS + wg * 128;
-          tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-          tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-          tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
-          tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
-          tmem_wait_ld();
-        }
-        const uint32_t p_tmem = lane_base + kTmemP + wg * 64;
+        const uint32_t s_tmem = lane_base + kTmemS + buf * 128 + wg * kCols;
         if (via_q && q == n - 1) {
           // ---- last tile of a Q-route item: P_l to shared memory, Q back through this S buffer ----
           // P_l (forward: rows scaled by lam, folded into the exponent) in the layout of the rhs buffer,
-          // written over K_i: s_full of the last tile implies that every S product has completed.
+          // written over K_i: s_full of the last tile implies that every S product has completed.  This
+          // group's columns sit inside one 64-column panel.
+          uint32_t v[kCols];
+#pragma unroll
+          for (int c = 0; c < kCols / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+          tmem_wait_ld();
           const float shift = (P.use_diag && !kReverse) ? __log2f(lam) : 0.0f;
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < kVec; ++c) {
             uint32_t o[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -510,94 +530,86 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
               const float e1 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + 2 * e + 1]), kLog2e, shift));
               o[e] = pack2_fast<kBf16>(e0, e1);
             }
-            *reinterpret_cast<uint4*>(s.ki + (c >> 3) * kHalfBytes + sw128_off(row, c & 7)) =
-                make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(my_ki + sw128_off(row, vec0 + c)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
           fence_proxy_async_smem();
           tc_fence_before_sync();
-          mbar_arrive(&s.pq_full);
+          mbar_arrive(&s.pq_full);          // all groups: S has been read, P_l is in shared memory
           if (!wait_barrier(&s.q_full, nq & 1, cta_abort, ctl, limit, chain, i, BAR_Q_FULL)) {
             alive = false;
             break;
           }
           tc_fence_after_sync();
-          {
-            const uint32_t s_tmem = lane_base + kTmemS + wg * 128;
-            tmem_ld32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-            tmem_ld32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-            tmem_ld32(s_tmem + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
-            tmem_ld32(s_tmem + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
-            tmem_wait_ld();
-          }
-          tc_fence_before_sync();
-          mbar_arrive(&s.s_free[wg]);       // only now may the next tile of this parity overwrite the buffer
-          if (!wait_barrier(&s.p_free[wg], ph ^ 1, cta_abort, ctl, limit, chain, i, BAR_P_FREE)) {
-            alive = false;
-            break;
-          }
-          tc_fence_after_sync();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < kCols / 32; ++c) tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+          tmem_wait_ld();
+          // -Q, rounded to 16 bits, over the first half of the columns just read
+#pragma unroll
+          for (int c = 0; c < kCols / 32; ++c) {
             uint32_t pk[16];
 #pragma unroll
             for (int e = 0; e < 16; ++e)
               pk[e] = pack2<kBf16>(-__uint_as_float(v[c * 32 + 2 * e]), -__uint_as_float(v[c * 32 + 2 * e + 1]));
-            tmem_st16(p_tmem + c * 16, pk);
+            tmem_st16(s_tmem + c * 16, pk);
           }
           tmem_wait_st();
           tc_fence_before_sync();
-          mbar_arrive(&s.p_full[wg]);       // -Q is in place for the closing product
+          mbar_arrive(&s.p_full[buf]);      // -Q is in place for the closing product
           if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
           continue;
         }
-        tc_fence_before_sync();
-        mbar_arrive(&s.s_free[wg]);
-        if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 46, gq);
-        // P[wg] was read by the P*Y product of two tiles ago
-        if (!wait_barrier(&s.p_free[wg], ph ^ 1, cta_abort, ctl, limit, chain, i, BAR_P_FREE)) {
-          alive = false;
-          break;
-        }
-        tc_fence_after_sync();
+        // Chunk c: columns 16c .. 16c+15 of this thread's range; its packed P lands on columns 8c .. 8c+7,
+        // inside chunks <= c, which are already in registers.
+        uint32_t sv[2][16];
+        tmem_ld16(s_tmem, sv[0]);
+        tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-          exp2_pack32<kBf16, false>(&v[c * 32], kLog2e, pk);
-          tmem_st16(p_tmem + c * 16, pk);
+        for (int c = 0; c < kCh; ++c) {
+          if (c + 1 < kCh) tmem_ld16(s_tmem + (c + 1) * 16, sv[(c + 1) & 1]);
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float e0 = ex2_mixed(__uint_as_float(sv[c & 1][2 * e]) * kLog2e, 2 * e);
+            const float e1 = ex2_mixed(__uint_as_float(sv[c & 1][2 * e + 1]) * kLog2e, 2 * e + 1);
+            pk[e] = pack2_fast<kBf16>(e0, e1);
+          }
+          if (c + 1 < kCh) tmem_wait_ld();
+          tmem_st8(s_tmem + c * 8, pk);
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&s.p_full[wg]);
+        mbar_arrive(&s.p_full[buf]);
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 41, gq);
       }
       if (!alive) break;
       g += n;
       if (via_q) ++nq;
 
-      // ---- epilogue: this group owns output columns 64*wg .. 64*wg+63 ----
+      // ---- epilogue: this group owns output columns kCols*wg .. + kCols-1 ----
       // Everything that does not depend on the accumulator is done before waiting for it: this
       // row-block's own right-hand side is read from shared memory now.
       if (!wait_barrier(&s.vi_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_VI_FULL)) break;
-      uint8_t* panel = s.rhs + wg * kHalfBytes;
-      uint4 vin[8];
+      uint8_t* panel = my_rhs;
+      uint4 vin[kVec];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) vin[c] = *reinterpret_cast<const uint4*>(panel + sw128_off(row, c));
+      for (int c = 0; c < kVec; ++c) vin[c] = *reinterpret_cast<const uint4*>(panel + sw128_off(row, vec0 + c));
       const float pre = (P.use_diag && !kReverse) ? lam : 1.0f;   // forward: rows scaled before X
       const float post = (P.use_diag && kReverse) ? lam : 1.0f;   // reverse: rows scaled after X^T
       typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
       elem_t* out_row = reinterpret_cast<elem_t*>(args.out) + (long long)b * args.out_strides.b +
                         (long long)(i * kBlock + row) * args.out_strides.n + (long long)h * args.out_strides.h +
-                        wg * 64;
-      uint32_t acc[64];
+                        wg * kCols;
+      uint32_t acc[kCols];
       if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FULL)) break;
       if ((via_q ? n - 1 : n) > 0) {      // tiles accumulated before the diagonal product
         tc_fence_after_sync();
-        tmem_ld32(lane_base + kTmemAcc + wg * 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
-        tmem_ld32(lane_base + kTmemAcc + wg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+#pragma unroll
+        for (int c = 0; c < kCols / 32; ++c)
+          tmem_ld32(lane_base + kTmemAcc + wg * kCols + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[c * 32]));
         tmem_wait_ld();
       } else {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) acc[e] = 0u;
+        for (int e = 0; e < kCols; ++e) acc[e] = 0u;
       }
       // The diagonal product is written over the accumulator, so with use_diag the accumulator is
       // released only after that product has been read back (below).
@@ -609,7 +621,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
       long long t_loop = 0;
       if (P.instrument && tid == 128) t_loop = (long long)globaltimer_ns();
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < kVec; ++c) {
         const uint32_t in[4] = {vin[c].x, vin[c].y, vin[c].z, vin[c].w};
         uint32_t o[4];
 #pragma unroll
@@ -620,7 +632,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           o[e] = pack2<kBf16>(r0, r1);
         }
         const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-        if (P.use_diag) *reinterpret_cast<uint4*>(panel + sw128_off(row, c)) = ov;
+        if (P.use_diag) *reinterpret_cast<uint4*>(panel + sw128_off(row, vec0 + c)) = ov;
         else *reinterpret_cast<uint4*>(out_row + c * 8) = ov;
       }
       fence_proxy_async_smem();
@@ -632,8 +644,9 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         if (!wait_barrier(&s.out_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_OUT_FULL)) break;
         tc_fence_after_sync();
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 44, 0);
-        tmem_ld32(lane_base + kTmemOut + wg * 64, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
-        tmem_ld32(lane_base + kTmemOut + wg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+#pragma unroll
+        for (int c = 0; c < kCols / 32; ++c)
+          tmem_ld32(lane_base + kTmemOut + wg * kCols + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[c * 32]));
         tmem_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(&s.acc_free);
@@ -642,13 +655,13 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         // releases the flag: a single bulk store and a release by a thread with nothing else in flight
         // publish faster than 256 threads' plain stores followed by GPU-scope fences.
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < kVec; ++c) {
           uint32_t o[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             o[e] = pack2<kBf16>(__uint_as_float(acc[c * 8 + 2 * e]) * post, __uint_as_float(acc[c * 8 + 2 * e + 1]) * post);
           }
-          *reinterpret_cast<uint4*>(panel + sw128_off(row, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(panel + sw128_off(row, vec0 + c)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
         fence_proxy_async_smem();
         mbar_arrive(&s.stage_full);
@@ -668,10 +681,10 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         }
       } else {
         // ---- publish (identity diagonal: the result was stored with plain stores above) ----
-        // Each warp orders its lanes' stores with a warp barrier and then adds 1 to the flag with release
-        // semantics at GPU scope; a consumer that acquires the value 8 observes all eight warps' stores.
+        // Each warp orders its lanes' stores with a warp barrier and then adds its share to the flag with
+        // release semantics at GPU scope; a consumer that acquires the full value observes all warps' stores.
         __syncwarp();
-        if (lane == 0) red_release_gpu_add(args.flags + chain * T + i, 1);
+        if (lane == 0) red_release_gpu_add(args.flags + chain * T + i, kFlagComplete / (4 * kG));
       }
       if (tid == 128) {
         LUCID_TR(args.trace, 3, trc, 45, i);
@@ -718,11 +731,11 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
 
 #ifndef LUCID_BODY_ONLY
 template <bool kBf16, bool kReverse>
-__global__ void __launch_bounds__(kSolveThreads, 1)
+__global__ void __launch_bounds__(solve_threads(kSolveGroups), 1)
 solve_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_in,
              const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_x,
              const __grid_constant__ CUtensorMap tm_st, const SolveArgs args) {
-  solve_body<kBf16, kReverse>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
+  solve_body<kBf16, kReverse, kSolveGroups>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -737,7 +750,7 @@ static cudaError_t launch_solve_t(const CUtensorMap& tm_k, const CUtensorMap& tm
   auto kern = solve_kernel<kBf16, kReverse>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem_bytes());
   if (e != cudaSuccess) return e;
-  kern<<<grid, kSolveThreads, solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
+  kern<<<grid, solve_threads(kSolveGroups), solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
   return cudaGetLastError();
 }
 
