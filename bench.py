@@ -171,6 +171,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--seqlen", type=int, default=WORKLOAD["N"], help="override N (parity/profiling runs only)")
+    ap.add_argument("--systems", type=int, default=0,
+                    help="use only the first K of the B*H (batch, head) systems (scaling studies only: "
+                         "--gpus 1 --systems 2 is one rank's share of the 8-GPU run)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -197,7 +200,7 @@ def main():
     lib = _cabi.load()
 
     B, N, H, D = WORKLOAD["B"], args.seqlen, WORKLOAD["H"], WORKLOAD["D"]
-    nsys = B * H
+    nsys = B * H if args.systems <= 0 else min(args.systems, B * H)
     lo, hi = shard_range(nsys, world, rank)
     n_local = hi - lo
     # each rank materialises only its own systems, as a (1, N, n_local, 128) BSHD tensor

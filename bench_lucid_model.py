@@ -115,13 +115,17 @@ class Model:
             k = rope(k.reshape(B, N, Hkv, D).transpose(1, 2), cos, sin)
             v = v.reshape(B, N, Hkv, D).transpose(1, 2)
             if is_global:
+                scale = None
                 if lucid:
-                    # call site of the reference: BSHD views, keys scaled by d^-1/4, V' = solve(k, v)
-                    k_bshd = (k * D ** -0.25).transpose(1, 2)          # strided BSHD view, no copy needed
-                    v_bshd = v.transpose(1, 2)
-                    v_prime = _forward_sub_fwd(k_bshd, v_bshd)
-                    k, v = k_bshd.transpose(1, 2), v_prime.transpose(1, 2)
-                a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+                    # call site of the reference (keys scaled by d^-1/4, V' = solve(k, v), attention on the
+                    # scaled keys) without its glue: the BHSD-backed tensors go in as strided BSHD views, the
+                    # key scale is folded into the solve and into the attention scale instead of being applied
+                    # to k in a pass of its own
+                    ks = D ** -0.25
+                    v_prime = _forward_sub_fwd(k.transpose(1, 2), v.transpose(1, 2), k_scale=ks)
+                    v = v_prime.transpose(1, 2)
+                    scale = ks / math.sqrt(D)                          # q . (ks k) / sqrt(d)
+                a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True, scale=scale)
             else:
                 a = sliding_window_attention(q, k, v, c["window"])
             x = x + a.transpose(1, 2).reshape(B, N, Hq * D) @ L["wo"].T

@@ -121,6 +121,21 @@ const char* lucid_status_string(int code);
 /* Sets the time limit (nanoseconds) of every device-side wait; default 2e9. */
 void lucid_set_wait_limit_ns(uint64_t ns);
 
+/* The same two operators for keys that the caller would otherwise scale first: the operator acts on
+ * k_scale * K (LUCID's call site uses k * d^-1/4, bench_lucid_model.py:164-170), the kernels read K as it is
+ * and fold k_scale^2 into the multiplier of every exponential; dK is the gradient with respect to the
+ * unscaled K (k_scale^2 times the accumulated product).  Saves the elementwise pass over K and the rounding
+ * of k_scale * K to 16 bits.  k_scale must be positive and finite; 1 gives lucid_fwd_sub / lucid_bwd_sub. */
+int lucid_fwd_sub_scaled(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D,
+                         int dtype, int flags, int window_blocks, int chain_group, float k_scale, void* workspace,
+                         size_t workspace_bytes, void* cuda_stream);
+int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prime, void* dv, void* dk,
+                         const int64_t k_strides[3], const int64_t vp_strides[3], const int64_t dvp_strides[3],
+                         const int64_t dv_strides[3], const int64_t dk_strides[3], int B, int N, int H, int D,
+                         int dtype, int flags, int mode, int chain_group, float k_scale, void* workspace,
+                         size_t workspace_bytes, void* cuda_stream);
+
 /* Scheduler knob: the first `steps` row-blocks of every (batch, head) system are scheduled for all systems
  * together (they are short and bound by the hand-over latency between consecutive row-blocks), the rest in
  * groups of `chain_group` systems; negative restores the default (0, i.e. groups from the start: the

@@ -29,7 +29,7 @@ _I64x3 = ctypes.c_int64 * 3
 EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_read_status",
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
            "lucid_profile_next_call", "lucid_set_head_steps", "lucid_fwd_sub_static",
-           "lucid_set_fused_backward")
+           "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled")
 
 
 class LucidKernelError(RuntimeError):
@@ -71,6 +71,15 @@ def load() -> ctypes.CDLL:
                                       _I64x3, _I64x3, _I64x3, _I64x3, _I64x3,
                                       c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
                                       c.c_void_p, c.c_size_t, c.c_void_p]
+        lib.lucid_fwd_sub_scaled.restype = c.c_int
+        lib.lucid_fwd_sub_scaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, _I64x3, _I64x3, _I64x3,
+                                             c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                                             c.c_int, c.c_float, c.c_void_p, c.c_size_t, c.c_void_p]
+        lib.lucid_bwd_sub_scaled.restype = c.c_int
+        lib.lucid_bwd_sub_scaled.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p, c.c_void_p,
+                                             _I64x3, _I64x3, _I64x3, _I64x3, _I64x3,
+                                             c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                                             c.c_int, c.c_float, c.c_void_p, c.c_size_t, c.c_void_p]
         lib.lucid_read_status.restype = c.c_int
         lib.lucid_read_status.argtypes = [c.c_void_p, c.c_void_p, c.POINTER(c.c_int32)]
         lib.lucid_status_string.restype = c.c_char_p
@@ -136,14 +145,14 @@ def _diag_key(k: torch.Tensor) -> tuple:
     return (k.data_ptr(), k._version, tuple(k.shape), tuple(k.stride()), k.dtype)
 
 
-def diag_is_cached(ws: torch.Tensor, k: torch.Tensor) -> bool:
+def diag_is_cached(ws: torch.Tensor, k: torch.Tensor, k_scale: float = 1.0) -> bool:
     entry = _diag_keys.get(ws.data_ptr())
-    return entry is not None and entry[0]() is k and entry[1] == _diag_key(k)
+    return entry is not None and entry[0]() is k and entry[1] == (_diag_key(k), float(k_scale))
 
 
-def diag_remember(ws: torch.Tensor, k: torch.Tensor, valid: bool) -> None:
+def diag_remember(ws: torch.Tensor, k: torch.Tensor, valid: bool, k_scale: float = 1.0) -> None:
     if valid:
-        _diag_keys[ws.data_ptr()] = (weakref.ref(k), _diag_key(k))
+        _diag_keys[ws.data_ptr()] = (weakref.ref(k), (_diag_key(k), float(k_scale)))
     else:
         _diag_keys.pop(ws.data_ptr(), None)
 

@@ -15,19 +15,22 @@ class LUCIDForwardSub(torch.autograd.Function):
     """``v_prime = LUCIDForwardSub.apply(k, v)`` with k, v in BSHD layout."""
 
     @staticmethod
-    def forward(ctx, k, v, block_size=128):
-        v_prime = _forward_sub_fwd(k, v, block_size=block_size, use_diag_solve=True)
+    def forward(ctx, k, v, block_size=128, k_scale=1.0):
+        v_prime = _forward_sub_fwd(k, v, block_size=block_size, use_diag_solve=True, k_scale=k_scale)
         ctx.save_for_backward(k, v_prime)
         ctx.block_size = block_size
+        ctx.k_scale = k_scale
         return v_prime
 
     @staticmethod
     def backward(ctx, dv_prime):
         k, v_prime = ctx.saved_tensors
         dv, dk = _forward_sub_bwd(k, v_prime, dv_prime, block_size=ctx.block_size, use_diag_solve=True,
-                                  use_combined_kernel=True)
-        return dk, dv, None
+                                  use_combined_kernel=True, k_scale=ctx.k_scale)
+        return dk, dv, None, None
 
 
-def lucid_forward_sub(k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    return LUCIDForwardSub.apply(k, v)
+def lucid_forward_sub(k: torch.Tensor, v: torch.Tensor, k_scale: float = 1.0) -> torch.Tensor:
+    """``k_scale``: the solve acts on ``k_scale * k`` (folded into the kernels); gradients are with respect
+    to ``k`` and ``v`` as passed."""
+    return LUCIDForwardSub.apply(k, v, 128, k_scale)

@@ -97,8 +97,10 @@ static int auto_group(int C, int N, int requested) {
   return (int)((C + ng - 1) / ng);
 }
 
-static Problem make_problem(int B, int N, int H, int flags, int window, int group) {
+static Problem make_problem(int B, int N, int H, int flags, int window, int group, float k_scale) {
   Problem p;
+  p.exp_scale = kLog2e * k_scale * k_scale;
+  p.out_scale = k_scale * k_scale;
   p.B = B;
   p.N = N;
   p.H = H;
@@ -153,6 +155,7 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
     pa.ctl = ctl + 0;
     pa.T = p.T;
     pa.H = p.H;
+    pa.exp_scale = p.exp_scale;
     pa.wait_ns = p.wait_ns;
     if ((e = launch_diag_prep(bf16, tm_k, pa, CT, stream)) != cudaSuccess) return (int)e;
   }
@@ -222,7 +225,16 @@ int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_s
                   const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D, int dtype,
                   int flags, int window_blocks, int chain_group, void* workspace, size_t workspace_bytes,
                   void* cuda_stream) {
+  return lucid_fwd_sub_scaled(k, v, v_prime, k_strides, v_strides, vp_strides, B, N, H, D, dtype, flags,
+                              window_blocks, chain_group, 1.0f, workspace, workspace_bytes, cuda_stream);
+}
+
+int lucid_fwd_sub_scaled(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D,
+                         int dtype, int flags, int window_blocks, int chain_group, float k_scale, void* workspace,
+                         size_t workspace_bytes, void* cuda_stream) {
   int rc;
+  if (!(k_scale > 0.0f) || !(k_scale < 1e18f)) return LUCID_E_BAD_SHAPE;
   if ((rc = check_shape(B, N, H, D, dtype))) return rc;
   if ((rc = check_tensor(k, k_strides)) || (rc = check_tensor(v, v_strides)) ||
       (rc = check_tensor(v_prime, vp_strides)))
@@ -235,7 +247,7 @@ int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_s
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);   // control words + flags
   if (e != cudaSuccess) return (int)e;
-  const Problem p = make_problem(B, N, H, flags, window_blocks, chain_group);
+  const Problem p = make_problem(B, N, H, flags, window_blocks, chain_group, k_scale);
   rc = run_solve(false, k, v, v_prime, k_strides, v_strides, vp_strides, p, dtype == LUCID_DTYPE_BF16, ws, lay,
                  stream);
   memset(g_events, 0, sizeof(g_events));
@@ -285,7 +297,18 @@ int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void
                   const int64_t k_strides[3], const int64_t vp_strides[3], const int64_t dvp_strides[3],
                   const int64_t dv_strides[3], const int64_t dk_strides[3], int B, int N, int H, int D, int dtype,
                   int flags, int mode, int chain_group, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  return lucid_bwd_sub_scaled(k, v_prime, dv_prime, dv, dk, k_strides, vp_strides, dvp_strides, dv_strides,
+                              dk_strides, B, N, H, D, dtype, flags, mode, chain_group, 1.0f, workspace,
+                              workspace_bytes, cuda_stream);
+}
+
+int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prime, void* dv, void* dk,
+                         const int64_t k_strides[3], const int64_t vp_strides[3], const int64_t dvp_strides[3],
+                         const int64_t dv_strides[3], const int64_t dk_strides[3], int B, int N, int H, int D,
+                         int dtype, int flags, int mode, int chain_group, float k_scale, void* workspace,
+                         size_t workspace_bytes, void* cuda_stream) {
   int rc;
+  if (!(k_scale > 0.0f) || !(k_scale < 1e18f)) return LUCID_E_BAD_SHAPE;
   if ((rc = check_shape(B, N, H, D, dtype))) return rc;
   if (mode != LUCID_BWD_DV_ONLY && mode != LUCID_BWD_COMBINED) return LUCID_E_BAD_SHAPE;
   if ((rc = check_tensor(k, k_strides)) || (rc = check_tensor(dv_prime, dvp_strides)) ||
@@ -303,7 +326,7 @@ int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void
   cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);
   if (e != cudaSuccess) return (int)e;
   const bool bf16 = dtype == LUCID_DTYPE_BF16;
-  const Problem p = make_problem(B, N, H, flags, 0, chain_group);
+  const Problem p = make_problem(B, N, H, flags, 0, chain_group, k_scale);
   const int sms = sm_count();
   if (sms <= 0) return LUCID_E_NO_DEVICE;
   const int CT = p.C * p.T;

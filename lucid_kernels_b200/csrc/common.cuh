@@ -41,6 +41,8 @@ struct Problem {
   int no_sync;       // skip flag waits (profiling only; results are then meaningless)
   int instrument;    // write per-row-block timestamps
   int reuse_diag;    // the workspace already holds X and lam_inv for this K (host decides)
+  float exp_scale;   // log2(e) * k_scale^2: the operator acts on k_scale * K, the kernels read K itself
+  float out_scale;   // k_scale^2: factor of dK with respect to the unscaled K
   unsigned long long wait_ns;  // time limit of every device-side wait
 };
 

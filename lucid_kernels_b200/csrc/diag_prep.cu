@@ -85,10 +85,10 @@ __global__ void __launch_bounds__(128) diag_prep_kernel(const __grid_constant__ 
   __syncthreads();   // also: the MMA has finished reading s.k
   if (ok) {
     const float srr = s.nt[tid][tid];
-    args.lam_inv[(long long)blk * kBlock + tid] = ex2_approx(-srr * kLog2e);
+    args.lam_inv[(long long)blk * kBlock + tid] = ex2_approx(-srr * args.exp_scale);
     for (int c = 0; c < kBlock; ++c) {
       const float v = s.nt[c][tid];
-      s.nt[c][tid] = (c < tid) ? ex2_approx((v - srr) * kLog2e) : 0.f;
+      s.nt[c][tid] = (c < tid) ? ex2_approx((v - srr) * args.exp_scale) : 0.f;
     }
   }
   __syncthreads();

@@ -361,6 +361,7 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
   } else if (warp >= 4) {
     // =========================== W = -exp(S) o G, then the dK epilogue ===========================
     const int wg = (warp - 4) >> 2;                  // column half: 64*wg .. 64*wg+63
+    const float xs = P.exp_scale;                    // exp(k_scale^2 * S) = exp2(S * xs)
     const int row = ((warp & 3) << 5) + lane;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     uint32_t g = 0;
@@ -422,8 +423,8 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           if ((C) < 3) tmem_ld16(s_tmem + ((C) + 1) * 16, NXT);                                        \
           uint32_t pk[8];                                                                              \
           _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                              \
-            const float e0 = ex2_approx(__uint_as_float(CUR[2 * e]) * kLog2e);                         \
-            const float e1 = ex2_approx(__uint_as_float(CUR[2 * e + 1]) * kLog2e);                     \
+            const float e0 = ex2_approx(__uint_as_float(CUR[2 * e]) * xs);                             \
+            const float e1 = ex2_approx(__uint_as_float(CUR[2 * e + 1]) * xs);                         \
             pk[e] = pack2_fast<kBf16>(-e0 * __uint_as_float(GV[(GOFF) + 2 * e]),                       \
                                       -e1 * __uint_as_float(GV[(GOFF) + 2 * e + 1]));                  \
           }                                                                                            \
@@ -464,7 +465,8 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           uint32_t o[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            o[e] = pack2<kBf16>(__uint_as_float(v[c * 8 + 2 * e]), __uint_as_float(v[c * 8 + 2 * e + 1]));
+            o[e] = pack2<kBf16>(__uint_as_float(v[c * 8 + 2 * e]) * P.out_scale,
+                                __uint_as_float(v[c * 8 + 2 * e + 1]) * P.out_scale);
           *reinterpret_cast<uint4*>(out_row + cc * 32 + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
         }
       }

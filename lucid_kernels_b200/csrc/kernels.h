@@ -20,6 +20,7 @@ struct PrepArgs {
   float* lam_inv;   // (C*T, 128)
   Control* ctl;
   int T, H;
+  float exp_scale;        // log2(e) * k_scale^2
   unsigned long long wait_ns;
 };
 

@@ -468,6 +468,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsExp));
     // =========================== exp groups + epilogue ===========================
     const int wg = (warp - 4) >> 2;                  // exp group: columns kCols*wg .. of every tile and of the output
+    const float xs = P.exp_scale;                    // exp(k_scale^2 * S) = exp2(S * xs)
     constexpr int kCh = kCols / 16;                  // 16-column chunks per thread and tile
     constexpr int kVec = kCols / 8;                  // 16-byte vectors of 16-bit values per thread and row
     uint8_t* const my_ki = s.ki + (wg * kCols / 64) * kHalfBytes;     // this group's 64-column panel ...
@@ -526,8 +527,8 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
             uint32_t o[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float e0 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + 2 * e]), kLog2e, shift));
-              const float e1 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + 2 * e + 1]), kLog2e, shift));
+              const float e0 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + 2 * e]), xs, shift));
+              const float e1 = ex2_approx(fmaf(__uint_as_float(v[c * 8 + 2 * e + 1]), xs, shift));
               o[e] = pack2_fast<kBf16>(e0, e1);
             }
             *reinterpret_cast<uint4*>(my_ki + sw128_off(row, vec0 + c)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -569,8 +570,8 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           uint32_t pk[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const float e0 = ex2_mixed(__uint_as_float(sv[c & 1][2 * e]) * kLog2e, 2 * e);
-            const float e1 = ex2_mixed(__uint_as_float(sv[c & 1][2 * e + 1]) * kLog2e, 2 * e + 1);
+            const float e0 = ex2_mixed(__uint_as_float(sv[c & 1][2 * e]) * xs, 2 * e);
+            const float e1 = ex2_mixed(__uint_as_float(sv[c & 1][2 * e + 1]) * xs, 2 * e + 1);
             pk[e] = pack2_fast<kBf16>(e0, e1);
           }
           if (c + 1 < kCh) tmem_wait_ld();

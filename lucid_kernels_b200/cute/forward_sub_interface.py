@@ -83,9 +83,14 @@ def _forward_sub_fwd(
     *,
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
+    k_scale: float = 1.0,
 ) -> torch.Tensor:
     """V'_i = inv(tril(exp(K_i K_i^T))) (V_i - sum_{j<i} exp(K_i K_j^T) V'_j)   (diagonal factor only
     with ``use_diag_solve``; with ``window_size=W`` only the last W blocks are subtracted).
+
+    ``k_scale`` (extension): the operator acts on ``k_scale * k`` without the caller having to form that
+    tensor (the reference's call site scales by ``d ** -0.25``, bench_lucid_model.py:164-170); the factor is
+    folded into the multiplier of the exponentials.
 
     Returns ``v_prime`` (same shape and dtype as ``v``), or ``(v_prime, timestamps)`` with
     ``instrument``; timestamps are int64 ``(batch*heads, T, 8)`` =
@@ -102,16 +107,17 @@ def _forward_sub_fwd(
         ws = _cabi.workspace(k.device, stream, B, N, H)
         flags = ((_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_NO_SYNC if no_sync else 0) |
                  (_cabi.FLAG_INSTRUMENT if instrument else 0))
-        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in):
+        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in, k_scale):
             flags |= _cabi.FLAG_REUSE_DIAG
-        rc = lib.lucid_fwd_sub(k.data_ptr(), v.data_ptr(), v_prime.data_ptr(), _cabi.strides3(k),
-                               _cabi.strides3(v), _cabi.strides3(v_prime), B, N, H, D, _cabi.dtype_code(k.dtype),
-                               flags, 0 if window_size is None else int(window_size),
-                               _GROUP_DEFAULT if chain_group is None else int(chain_group),
-                               ws.data_ptr(), ws.numel(), stream)
+        rc = lib.lucid_fwd_sub_scaled(k.data_ptr(), v.data_ptr(), v_prime.data_ptr(), _cabi.strides3(k),
+                                      _cabi.strides3(v), _cabi.strides3(v_prime), B, N, H, D,
+                                      _cabi.dtype_code(k.dtype), flags,
+                                      0 if window_size is None else int(window_size),
+                                      _GROUP_DEFAULT if chain_group is None else int(chain_group),
+                                      float(k_scale), ws.data_ptr(), ws.numel(), stream)
         _cabi.check_rc(rc, "lucid_fwd_sub")
         # the inverses now in the workspace belong to k_in, provided the kernels read k_in's own storage
-        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr())
+        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr(), k_scale)
         if _CHECK_DEFAULT if check is None else check:
             _cabi.raise_on_device_error(ws, stream, "_forward_sub_fwd")
     if instrument:
@@ -119,7 +125,8 @@ def _forward_sub_fwd(
     return v_prime
 
 
-def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, chain_group, what, k_in=None):
+def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, chain_group, what, k_in=None,
+              k_scale=1.0):
     B, N, H, D = k.shape
     k_in = k if k_in is None else k_in
     lib = _cabi.load()
@@ -129,19 +136,19 @@ def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, cha
     with torch.cuda.device(k.device):
         ws = _cabi.workspace(k.device, stream, B, N, H)
         flags = (_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_INSTRUMENT if instrument else 0)
-        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in):
+        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in, k_scale):
             flags |= _cabi.FLAG_REUSE_DIAG
         vp_ptr = v_prime.data_ptr() if v_prime is not None else None
         vp_str = _cabi.strides3(v_prime) if v_prime is not None else _cabi.strides3(k)
-        rc = lib.lucid_bwd_sub(k.data_ptr(), vp_ptr, dv_prime.data_ptr(), dv.data_ptr(),
-                               dk.data_ptr() if dk is not None else None,
-                               _cabi.strides3(k), vp_str, _cabi.strides3(dv_prime), _cabi.strides3(dv),
-                               _cabi.strides3(dk) if dk is not None else _cabi.strides3(dv),
-                               B, N, H, D, _cabi.dtype_code(k.dtype), flags, mode,
-                               _GROUP_DEFAULT if chain_group is None else int(chain_group),
-                               ws.data_ptr(), ws.numel(), stream)
+        rc = lib.lucid_bwd_sub_scaled(k.data_ptr(), vp_ptr, dv_prime.data_ptr(), dv.data_ptr(),
+                                      dk.data_ptr() if dk is not None else None,
+                                      _cabi.strides3(k), vp_str, _cabi.strides3(dv_prime), _cabi.strides3(dv),
+                                      _cabi.strides3(dk) if dk is not None else _cabi.strides3(dv),
+                                      B, N, H, D, _cabi.dtype_code(k.dtype), flags, mode,
+                                      _GROUP_DEFAULT if chain_group is None else int(chain_group),
+                                      float(k_scale), ws.data_ptr(), ws.numel(), stream)
         _cabi.check_rc(rc, what)
-        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr())
+        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr(), k_scale)
         if _CHECK_DEFAULT if check is None else check:
             _cabi.raise_on_device_error(ws, stream, what)
     ts = _timestamps_view(ws, B, N, H).clone() if instrument else None
@@ -157,6 +164,7 @@ def _forward_sub_bwd_dv(
     *,
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
+    k_scale: float = 1.0,
 ) -> torch.Tensor:
     """dV_i = inv(tril(exp(K_i K_i^T)))^T (dV'_i - sum_{j>i} exp(K_i K_j^T) dV_j), solved from the last
     block to the first."""
@@ -165,7 +173,7 @@ def _forward_sub_bwd_dv(
     k_in = k
     k, dv_prime = _aligned(k.detach()), _aligned(dv_prime.detach())
     dv, _, ts = _bwd_call(k, None, dv_prime, _cabi.BWD_DV_ONLY, use_diag_solve, instrument, check, chain_group,
-                          "_forward_sub_bwd_dv", k_in=k_in)
+                          "_forward_sub_bwd_dv", k_in=k_in, k_scale=k_scale)
     if instrument:
         return dv, ts
     return dv
@@ -181,14 +189,16 @@ def _forward_sub_bwd_combined(
     *,
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
+    k_scale: float = 1.0,
 ) -> tuple:
-    """(dv, dk).  Unlike the reference, ``dk`` already contains the diagonal-block term."""
+    """(dv, dk).  Unlike the reference, ``dk`` already contains the diagonal-block term.  With ``k_scale``
+    the operator acts on ``k_scale * k`` and ``dk`` is the gradient with respect to ``k`` itself."""
     k, v_prime, dv_prime = [maybe_contiguous(t) for t in (k, v_prime, dv_prime)]
     _common_asserts(k, (v_prime, dv_prime), block_size)
     k_in = k
     k, v_prime, dv_prime = [_aligned(t.detach()) for t in (k, v_prime, dv_prime)]
     dv, dk, ts = _bwd_call(k, v_prime, dv_prime, _cabi.BWD_COMBINED, use_diag_solve, instrument, check,
-                           chain_group, "_forward_sub_bwd_combined", k_in=k_in)
+                           chain_group, "_forward_sub_bwd_combined", k_in=k_in, k_scale=k_scale)
     if instrument:
         return dv, dk, ts
     return dv, dk
@@ -204,9 +214,11 @@ def _forward_sub_bwd(
     *,
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
+    k_scale: float = 1.0,
 ) -> tuple:
     """Full backward pass: returns ``(dv, dk)``, gradients w.r.t. V and K.  Both settings of
     ``use_combined_kernel`` run the same device kernels here."""
     del use_combined_kernel
     return _forward_sub_bwd_combined(k, v_prime, dv_prime, block_size=block_size,
-                                     use_diag_solve=use_diag_solve, check=check, chain_group=chain_group)
+                                     use_diag_solve=use_diag_solve, check=check, chain_group=chain_group,
+                                     k_scale=k_scale)

@@ -191,6 +191,35 @@ def test_backward_in_one_launch_matches_separate_launches(ops, dtype, H):
     assert bool(torch.isfinite(dk0.float()).all())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_key_scale_folded_into_the_kernels(ops, dtype):
+    """k_scale: the operator acts on k_scale * k while the kernels read k itself.  Checked against the fp64
+    oracle on k_scale * k (same 16-bit k), with dK chained back to the unscaled k; and the autograd wrapper
+    hands the same gradients out."""
+    from lucid_kernels_b200 import lucid_forward_sub
+
+    s = 128 ** -0.25
+    Ks, V, G = orc.make_inputs(2, 1024, 2, dtype=torch.float32, seed=3)
+    K = (Ks / s).to(dtype)                                    # unscaled keys, N(0, 1), rounded to 16 bits
+    V, G = V.to(dtype), G.to(dtype)
+    Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+    vp = ops._forward_sub_fwd(Kc, Vc, k_scale=s, check=True)
+    dv, dk = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, k_scale=s, check=True)
+    rvp, rdv, rdk_scaled = orc.dense_fwd_bwd(K.double() * s, V, G)
+    assert orc.rel_err(vp, rvp) < 0.01
+    assert orc.rel_err(dv, rdv) < 0.01
+    assert orc.rel_err(dk, rdk_scaled * s) < 0.02
+    # a different scale on the same k must not reuse the diagonal inverses of the first call
+    vp2 = ops._forward_sub_fwd(Kc, Vc, k_scale=0.5 * s, check=True)
+    rvp2 = orc.forward_sub_dense(K.double() * (0.5 * s), V.double())
+    assert orc.rel_err(vp2, rvp2) < 0.01
+    # autograd wrapper
+    Kg, Vg = Kc.clone().requires_grad_(True), Vc.clone().requires_grad_(True)
+    out = lucid_forward_sub(Kg, Vg, k_scale=s)
+    (out.float() * Gc.float()).sum().backward()
+    assert torch.equal(out.detach(), vp) and torch.equal(Vg.grad, dv) and torch.equal(Kg.grad, dk)
+
+
 def test_argument_errors(ops):
     K, V, _ = orc.make_inputs(1, 256, 1, dtype=torch.bfloat16)
     with pytest.raises(AssertionError):
