@@ -1,5 +1,5 @@
 // Backward pass in one launch for problems with few chains per GPU: the reverse solve is then bound by
-// its chain latency (T publish -> acquire rounds) and leaves most SMs idle, while the dK kernel that
+// its chain latency (T publish -> acquire hand-overs) and leaves most SMs idle, while the dK kernel that
 // follows is bound by throughput.  Here CTAs 0 .. n_solve-1 run the reverse solve (and join the dK program
 // when the solve's row-blocks have all been taken) and the other CTAs run the dK program from the start,
 // each dK row-block waiting (bounded) for the solve's flag of that row-block.  All CTAs of

@@ -12,8 +12,8 @@
 // increment per storing warp).  Consumers acquire the complete flag before their TMA load of Y_i.
 //
 // Critical path.  A chain advances one row-block per "publish -> flag -> load -> finish -> publish"
-// round, so everything that does not need the newest predecessor Y_l (l = i-1 forward, i+1 reverse) is
-// taken off that round.  With P_l = exp(K_i K_l^T) and A = X_i (forward, rows of the right-hand side
+// hand-over, so everything that does not need the newest predecessor Y_l (l = i-1 forward, i+1 reverse) is
+// taken off that hand-over.  With P_l = exp(K_i K_l^T) and A = X_i (forward, rows of the right-hand side
 // scaled by lam) or X_i^T (reverse, result rows scaled by lam),
 //     Y_i = A (Y_in_i - sum_{j != l} P_j Y_j) - (A P_l) Y_l  =  z - Q Y_l,
 // and both z and Q = A P_l are formed while Y_l is still being computed by another CTA: P_l goes to
