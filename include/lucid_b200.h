@@ -150,6 +150,12 @@ void lucid_set_head_steps(int steps);
  * launch (forward_sub_bwd.py:1053-1269). */
 void lucid_set_fused_backward(int max_chains, int solve_ctas);
 
+/* Solves with at most `max_chains` (batch, head) systems (and an even number of 128-row blocks, the diagonal
+ * solve, no window) run as clusters of two CTAs that solve pairs of consecutive row-blocks and hand the first
+ * result to the second through shared memory; 0 disables it.  Default 8.  No counterpart in the reference,
+ * which publishes every row-block through global memory (forward_sub_fwd.py:536-544). */
+void lucid_set_pair_solve(int max_chains);
+
 /* Per-kernel timing for benchmarks: the NEXT lucid_fwd_sub / lucid_bwd_sub call records these
  * cudaEvent_t handles on its stream (before the diagonal-prep kernel, after it, after the solve kernel,
  * after the dK kernel); any of them may be NULL.  The handles are forgotten after that call.  Stands in

@@ -29,7 +29,8 @@ _I64x3 = ctypes.c_int64 * 3
 EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_read_status",
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
            "lucid_profile_next_call", "lucid_set_head_steps", "lucid_fwd_sub_static",
-           "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled")
+           "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled",
+           "lucid_set_pair_solve")
 
 
 class LucidKernelError(RuntimeError):
@@ -86,6 +87,10 @@ def load() -> ctypes.CDLL:
         lib.lucid_status_string.argtypes = [c.c_int]
         lib.lucid_set_head_steps.restype = None
         lib.lucid_set_head_steps.argtypes = [c.c_int]
+        lib.lucid_set_pair_solve.restype = None
+        lib.lucid_set_pair_solve.argtypes = [c.c_int]
+        if os.environ.get("LUCID_B200_PAIR_SOLVE"):
+            lib.lucid_set_pair_solve(int(os.environ["LUCID_B200_PAIR_SOLVE"]))
         lib.lucid_set_fused_backward.restype = None
         lib.lucid_set_fused_backward.argtypes = [c.c_int, c.c_int]
         # LUCID_B200_FUSED_BWD="max_chains[,solve_ctas]" overrides the library's default (4, automatic)

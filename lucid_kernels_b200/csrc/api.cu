@@ -14,6 +14,7 @@ static cudaEvent_t g_events[4] = {nullptr, nullptr, nullptr, nullptr};
 static long long* g_trace = nullptr;
 static int g_fuse_max_chains = 2;   // combined backward: fuse solve and dK into one launch up to this many chains
 static int g_fuse_solve_ctas = 0;   // 0 = automatic share
+static int g_pair_max_chains = 8;   // solve pairs of row-blocks with clusters of two CTAs up to this many chains
 static int g_head = -1;   // scheduler knob; < 0 = default
 static inline void record_event(int i, cudaStream_t stream) {
   if (g_events[i]) cudaEventRecord(g_events[i], stream);
@@ -178,7 +179,20 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
     e = launch_bwd_fused(bf16, tm_k, tm_in, tm_out, tm_x, tm_st, fused->tm_vp, fused->tm_dv, sa, fused->args,
                          fused->n_solve, sms, stream);
   } else {
-    e = launch_solve(bf16, reverse, tm_k, tm_in, tm_out, tm_x, tm_st, sa, grid, stream);
+    // Few chains: the hand-over latency between consecutive row-blocks limits the solve; pairs of row-blocks
+    // are then solved by clusters of two CTAs, the first handing its result to the second through shared memory.
+    // Worth it only while the chain latency, not the tile throughput, bounds the solve: about C * T <= 768
+    // on B200 (forward, ms, pairs against single row-blocks: 8 chains of N=8192 0.255 / 0.270, 1 and 2 chains of
+    // N=32768 0.82 / 0.93 and 0.95 / 1.00, but 4 chains of N=65536 5.5 / 4.9 - the pairs are taken in a fixed
+    // rotation, which balances the tile work less well than the ticket counter).
+    const bool pair = p.C <= g_pair_max_chains && p.C * p.T <= 768 && p.use_diag && p.window <= 0 && !p.no_sync &&
+                      (p.T % 2) == 0 && p.head == 0;
+    int pgrid = grid;
+    if (pair) {
+      const int items = CT / 2;
+      pgrid = 2 * (items < sms / 2 ? items : sms / 2);
+    }
+    e = launch_solve(bf16, reverse, pair, tm_k, tm_in, tm_out, tm_x, tm_st, sa, pair ? pgrid : grid, stream);
   }
   if (e != cudaSuccess) return (int)e;
   record_event(2, stream);
@@ -204,6 +218,8 @@ size_t lucid_workspace_timestamps_offset(int B, int N, int H) {
 void lucid_set_wait_limit_ns(uint64_t ns) { g_wait_ns = ns; }
 
 void lucid_set_head_steps(int steps) { g_head = steps; }
+
+void lucid_set_pair_solve(int max_chains) { g_pair_max_chains = max_chains; }
 
 void lucid_set_fused_backward(int max_chains, int solve_ctas) {
   g_fuse_max_chains = max_chains;

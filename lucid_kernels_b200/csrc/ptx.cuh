@@ -69,11 +69,81 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// thread-block clusters: the peer CTA's shared memory and barriers (no multicast loads anywhere)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of the peer CTA's copy of a shared-memory location of this CTA
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint4 v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+// arrive on a barrier of the peer CTA; releases this thread's earlier writes at cluster scope
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// arrive on a barrier of this CTA with a cluster-scope release (its waiter may be signalled on to the peer)
+__device__ __forceinline__ void mbar_arrive_rel_cluster(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// poll a barrier of this CTA that the peer CTA (or a thread relaying the peer's data) arrives on; the
+// non-blocking test, because a suspended try_wait was not woken promptly by arrivals from the other SM
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bulk copy from this CTA's shared memory into the peer's (no multicast); completion is counted in bytes on
+// a barrier of the peer, like a TMA load there.  All addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_local_addr, uint32_t bytes,
+                                                  uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   dst_cluster_addr),
+               "r"(src_local_addr), "r"(bytes), "r"(bar_cluster_addr)
+               : "memory");
+}
+// a word in the peer CTA's shared memory, written with release / read with acquire at cluster scope
+__device__ __forceinline__ void st_release_cluster(uint32_t cluster_addr, int v) {
+  asm volatile("st.release.cluster.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_cluster_local(const int* p) {
+  int v;
+  asm volatile("ld.acquire.cluster.shared::cta.b32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+// all threads of both CTAs: nobody passes before everybody has arrived (start: the peer's barriers are
+// initialised; end: the peer no longer touches this CTA's shared memory)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // fences
 // ---------------------------------------------------------------------------------------------
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma operands)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// the same for writes into the shared memory of any CTA of the cluster
+__device__ __forceinline__ void fence_proxy_async_cluster_smem() {
+  asm volatile("fence.proxy.async.shared::cluster;" ::: "memory");
 }
 // generic <-> async proxy ordering for global memory (flag acquire, then TMA load of the tile)
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }

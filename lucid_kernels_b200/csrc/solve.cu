@@ -21,6 +21,14 @@
 // more diagonal product, Q comes back through the idle S buffer, is negated, rounded to 16 bits and parked
 // in the idle P buffer.  Once Y_l has arrived a single product OUT += (-Q) Y_l finishes the row-block.
 //
+// Pair mode (few chains, where the hand-over latency between consecutive row-blocks is what limits a
+// chain): the grid is launched as clusters of two CTAs, work items are pairs of consecutive row-blocks of
+// a chain taken in a fixed rotation by the clusters, CTA 0 of a cluster solves the first row-block and
+// CTA 1 the second.  CTA 0 hands its result to CTA 1 directly: its epilogue threads write the tile into
+// the ring stages CTA 1 has claimed for it (st.shared::cluster) and one thread arrives on CTA 1's
+// barriers, which replaces "TMA store, release the flag, acquire it, TMA load" for every second
+// hand-over of the chain.  CTA 0 still stores and publishes the tile for all later row-blocks.
+//
 // Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 issues the
 // S products and owns TMEM, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warp 3 issues the
 // P*Y and diagonal products, warps 4-7 / 8-11 two exp groups that split every tile's columns (64 each)
@@ -48,16 +56,18 @@ struct SolveSmem {
   uint64_t ki_full, ki_free, x_full, vi_full, xr_free, r_free, stage_full;
   uint64_t s_full[3], sbuf_free[3], p_full[3];
   uint64_t acc_full, acc_free, rhs_full, out_full, pq_full, q_full;
+
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
   uint32_t tmem_base;
   int abort_flag;
+  int peer_items;        // pair mode, CTA 0: items for whose handed-over tile CTA 1 has claimed its ring stages
 };
 
 enum SolveBar : int {
   BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
   BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
-  BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL, BAR_PQ_FULL, BAR_Q_FULL
+  BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL, BAR_PQ_FULL, BAR_Q_FULL, BAR_PEER_READY
 };
 
 // Block size: four service warps plus kG exp groups of four warps (128 threads, one per row).
@@ -78,7 +88,7 @@ template <> struct SolveRegs<4> { static constexpr int service = 64, exp = 104, 
 
 // The whole CTA program, callable from more than one kernel (the tensor maps must be __grid_constant__
 // parameters of the calling kernel).
-template <bool kBf16, bool kReverse, int kG>
+template <bool kBf16, bool kReverse, int kG, bool kPair = false>
 __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, box 64 x 128
                                            const CUtensorMap& tm_in,    // V (or dV'), box 64 x 128
                                            const CUtensorMap& tm_out,   // Y, box 64 x 64
@@ -111,7 +121,8 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     mbar_init(&s.x_full, 1);
     mbar_init(&s.vi_full, 1);
     mbar_init(&s.xr_free, 1);
-    mbar_init(&s.r_free, 1);
+    // pair mode, first CTA: the staged tile is also copied to the peer, which acknowledges receipt
+    mbar_init(&s.r_free, (kPair && cluster_ctarank() == 0) ? 2 : 1);
     mbar_init(&s.stage_full, kExpThreads);
     for (int i = 0; i < 3; ++i) {
       mbar_init(&s.s_full[i], 1);
@@ -129,6 +140,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     mbar_init(&s.pq_full, kExpThreads);
     mbar_init(&s.q_full, 1);
     s.abort_flag = 0;
+    s.peer_items = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -138,6 +150,9 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
   }
   tc_fence_before_sync();
   __syncthreads();
+  // pair mode: the peer's barriers exist before anybody arrives on them
+  const uint32_t crank = kPair ? cluster_ctarank() : 0u;
+  if (kPair) cluster_sync_all();
   // tracing builds: wall time and SM cycles at the start and end of this CTA (role 6) give the SM clock
   {
     int slot6 = (kReverse ? 2 : 0);
@@ -152,7 +167,14 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
   // S buffer g % 3 in phase (g / 3) & 1.
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& jfirst) -> bool {
     int step;
-    if (!decode_ticket(ticket, P.C, T, P.group, P.head, chain, step)) return false;
+    if (kPair) {
+      // a work item is a pair of consecutive row-blocks (T is even): this CTA solves the first or second
+      int ps;
+      if (!decode_ticket(ticket, P.C, T >> 1, P.group, 0, chain, ps)) return false;
+      step = 2 * ps + (int)crank;
+    } else if (!decode_ticket(ticket, P.C, T, P.group, P.head, chain, step)) {
+      return false;
+    }
     if (kReverse) {
       i = T - 1 - step;
       n = step;           // blocks i+1 .. T-1, visited from T-1 down to i+1
@@ -184,7 +206,9 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_empty[slot], ((it >> 1) & 1) ^ 1, cta_abort, ctl, limit, -1, -1, BAR_TK_EMPTY)) break;
-        const int ticket = atomicAdd(&ctl->ticket, 1);
+        // pair mode: both CTAs of a cluster must work on the same pair, so the clusters take the pairs in a
+        // fixed rotation (dependency order is preserved: a cluster's items have increasing tickets)
+        const int ticket = kPair ? (int)(blockIdx.x >> 1) + it * (int)(gridDim.x >> 1) : atomicAdd(&ctl->ticket, 1);
         s.tk_slot[slot] = ticket;
         mbar_arrive(&s.tk_full[slot]);
         int chain, i, n, jfirst;
@@ -261,6 +285,15 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
               !wait_barrier(&s.v_empty[st1], (((u + 1) >> 2) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_V_EMPTY)) {
             alive = false;
             break;
+          }
+          if (kPair && crank == 1 && q == n - 1) {
+            // The newest predecessor is the row-block the peer CTA is solving: it writes the tile into the
+            // two stages just claimed and arrives on their barriers itself.
+            mbar_expect_tx(&s.v_full[st0], kHalfBytes);
+            mbar_expect_tx(&s.v_full[st1], kHalfBytes);
+            st_release_cluster(mapa_u32(smem_u32(&s.peer_items), 0), it + 1);
+            u += 2;
+            continue;
           }
           if (!P.no_sync) {
             if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j,
@@ -397,6 +430,9 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
             const uint32_t u = gq * 2 + half;
             const uint32_t st = u & 3;
             if (!wait_barrier(&s.v_full[st], (u >> 2) & 1, cta_abort, ctl, limit, chain, i, BAR_V_FULL)) return false;
+            // pair mode: the handed-over tile has arrived (second half), the peer may reuse its staging buffer
+            if (kPair && fold && crank == 1 && half == 1 && elect_one())
+              mbar_arrive_cluster(mapa_u32(smem_u32(&s.r_free), 0));
             tc_fence_after_sync();
             if (leader) LUCID_TR(args.trace, 5, trc, 33, u);
             const uint64_t db = d_vr0 + st * (kHalfBytes >> 4);
@@ -414,14 +450,18 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           if (leader) LUCID_TR(args.trace, 5, trc, 34, gq);
           return true;
         };
-        for (int q = 0; q < n_acc; ++q) {
+        // Pair mode: a chain's row-blocks are published in quick pairs, so the last TWO predecessors of a
+        // row-block arrive late and close together; Q, which needs no Y at all, is therefore formed before
+        // the last accumulated tile instead of after it.
+        const int n_early = (kPair && via_q && n_acc >= 1) ? n_acc - 1 : n_acc;
+        for (int q = 0; q < n_early; ++q) {
           if (!issue_py(g + q, q == 0, false)) {
             alive = false;
             break;
           }
         }
         if (!alive) break;
-        umma_commit_w(&s.acc_full);
+        if (n_early == n_acc) umma_commit_w(&s.acc_full);
         if (via_q) {
           // Q = X(^T) P_l into the S buffer the last tile came from (its group has drained it)
           if (!wait_barrier(&s.pq_full, nq & 1, cta_abort, ctl, limit, chain, i, BAR_PQ_FULL)) break;
@@ -436,6 +476,10 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           }
           umma_commit_w(&s.q_full);
           umma_commit_w(&s.ki_free);
+        }
+        if (n_early < n_acc) {
+          if (!issue_py(g + n_acc - 1, n_acc == 1, false)) break;
+          umma_commit_w(&s.acc_full);
         }
         // diagonal step
         if (!wait_barrier(&s.rhs_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_RHS_FULL)) break;
@@ -478,6 +522,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     uint32_t g = 0;
     uint32_t nq = 0;             // items finished through Q so far (phase of pq_full / q_full)
+    uint32_t u_peer = 0;         // pair mode, CTA 0: half-tiles the peer CTA's rings have seen so far
     bool alive = true;
     int trc = 0;
     (void)trc;
@@ -655,6 +700,36 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         // the TMA store expects, and one thread stores the tile, waits for the store to complete and
         // releases the flag: a single bulk store and a release by a thread with nothing else in flight
         // publish faster than 256 threads' plain stores followed by GPU-scope fences.
+        // Pair mode, CTA 0: the same values also go straight into the peer CTA's ring, into the two stages
+        // it has claimed for its last tile (rows 0-63 and 64-127 of the tile, two 64-column panels each).
+        uint32_t st0 = 0, st1 = 0;
+        const bool hand_over = kPair && crank == 0;
+        if (hand_over) {
+          const uint32_t u_last = u_peer + 2 * (uint32_t)n;          // the peer's item has n + 1 tiles
+          st0 = u_last & 3;
+          st1 = (u_last + 1) & 3;
+          u_peer = u_last + 2;
+          // a counter, not a barrier phase: the peer's producer may run an item ahead.  One lane per warp
+          // polls (cluster-scope acquire loads are expensive), the warp barrier passes the result on.
+          int ok = 1;
+          if (lane == 0 && ld_acquire_cluster_local(&s.peer_items) <= it) {
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (ld_acquire_cluster_local(&s.peer_items) <= it) {
+              if ((++spins & 63u) == 0) {
+                if (*cta_abort) { ok = 0; break; }
+                if (globaltimer_ns() - t0 > limit) {
+                  *cta_abort = 1;
+                  report_error(ctl, kErrBarrierTimeout, chain, i, 0, BAR_PEER_READY);
+                  ok = 0;
+                  break;
+                }
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+        }
 #pragma unroll
         for (int c = 0; c < kVec; ++c) {
           uint32_t o[4];
@@ -664,10 +739,28 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           }
           *reinterpret_cast<uint4*>(panel + sw128_off(row, vec0 + c)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
+        // local staging: read by the TMA store (async proxy).  The peer's copy is fenced on the peer's side,
+        // after it has acquired the barrier: a cluster-wide proxy fence here cost 4000 cycles per row-block.
         fence_proxy_async_smem();
         mbar_arrive(&s.stage_full);
         if (tid == 128) {
-          if (!wait_barrier(&s.stage_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_STAGE_FULL)) break;
+          if (hand_over) {
+            if (!wait_barrier(&s.stage_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_STAGE_FULL)) break;
+            // The staged tile (two 64-column panels of 128 rows) goes to the peer as four 8 KiB bulk copies:
+            // rows 0-63 of both panels into stage st0, rows 64-127 into st1 - the layout of a ring stage, and
+            // the swizzle pattern repeats every 8 rows, so the bytes are copied as they are.  Their arrival
+            // completes the peer's stage barriers like a TMA load; the peer acknowledges on r_free.
+#pragma unroll
+            for (int hp = 0; hp < 4; ++hp) {
+              const uint32_t half_rows = hp >> 1, pnl = hp & 1;
+              const uint32_t st = half_rows ? st1 : st0;
+              bulk_copy_to_peer(mapa_u32(smem_u32(s.vring[st]) + pnl * 8192u, 1),
+                                smem_u32(s.rhs) + pnl * kHalfBytes + half_rows * 8192u, 8192u,
+                                mapa_u32(smem_u32(&s.v_full[st]), 1));
+            }
+          } else if (!wait_barrier(&s.stage_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_STAGE_FULL)) {
+            break;
+          }
           LUCID_TR(args.trace, 3, trc, 47, i);
           tma_store_4d(&tm_st, s.rhs, 0, i * kBlock, h, b);
           tma_store_4d(&tm_st, s.rhs + kHalfBytes, 64, i * kBlock, h, b);
@@ -717,6 +810,8 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
+  // pair mode: the peer no longer writes into this CTA's shared memory or arrives on its barriers
+  if (kPair) cluster_sync_all();
   if (!last_program) {
     // Another CTA program follows in the same kernel: it lays its own barriers over this memory, and its
     // warps run with the kernel's launch-time register count again (the exp warpgroups give back what the
@@ -731,12 +826,12 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
 }
 
 #ifndef LUCID_BODY_ONLY
-template <bool kBf16, bool kReverse>
+template <bool kBf16, bool kReverse, bool kPair>
 __global__ void __launch_bounds__(solve_threads(kSolveGroups), 1)
 solve_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_in,
              const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_x,
              const __grid_constant__ CUtensorMap tm_st, const SolveArgs args) {
-  solve_body<kBf16, kReverse, kSolveGroups>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
+  solve_body<kBf16, kReverse, kSolveGroups, kPair>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -744,26 +839,50 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ C
 // ---------------------------------------------------------------------------------------------
 size_t solve_smem_bytes() { return sizeof(SolveSmem) + 1024; }
 
-template <bool kBf16, bool kReverse>
+template <bool kBf16, bool kReverse, bool kPair>
 static cudaError_t launch_solve_t(const CUtensorMap& tm_k, const CUtensorMap& tm_in, const CUtensorMap& tm_out,
                                   const CUtensorMap& tm_x, const CUtensorMap& tm_st, const SolveArgs& args, int grid,
                                   cudaStream_t stream) {
-  auto kern = solve_kernel<kBf16, kReverse>;
+  auto kern = solve_kernel<kBf16, kReverse, kPair>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem_bytes());
   if (e != cudaSuccess) return e;
-  kern<<<grid, solve_threads(kSolveGroups), solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
-  return cudaGetLastError();
+  if (!kPair) {
+    kern<<<grid, solve_threads(kSolveGroups), solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
+    return cudaGetLastError();
+  }
+  // clusters of two CTAs; every cluster of the grid must be resident (the CTAs wait for one another)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(solve_threads(kSolveGroups));
+  cfg.dynamicSmemBytes = solve_smem_bytes();
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int max_clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+  if (e != cudaSuccess) return e;
+  if (max_clusters < 1) return cudaErrorLaunchOutOfResources;
+  if (grid > 2 * max_clusters) cfg.gridDim = dim3(2 * max_clusters);
+  return cudaLaunchKernelEx(&cfg, kern, tm_k, tm_in, tm_out, tm_x, tm_st, args);
 }
 
-cudaError_t launch_solve(bool bf16, bool reverse, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
+cudaError_t launch_solve(bool bf16, bool reverse, bool pair, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
                          const CUtensorMap& tm_out, const CUtensorMap& tm_x, const CUtensorMap& tm_st,
                          const SolveArgs& args, int grid, cudaStream_t stream) {
+#define LUCID_LAUNCH(BF, REV, PAIR) \
+  launch_solve_t<BF, REV, PAIR>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
   if (bf16) {
-    return reverse ? launch_solve_t<true, true>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
-                   : launch_solve_t<true, false>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream);
+    if (pair) return reverse ? LUCID_LAUNCH(true, true, true) : LUCID_LAUNCH(true, false, true);
+    return reverse ? LUCID_LAUNCH(true, true, false) : LUCID_LAUNCH(true, false, false);
   }
-  return reverse ? launch_solve_t<false, true>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
-                 : launch_solve_t<false, false>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream);
+  if (pair) return reverse ? LUCID_LAUNCH(false, true, true) : LUCID_LAUNCH(false, false, true);
+  return reverse ? LUCID_LAUNCH(false, true, false) : LUCID_LAUNCH(false, false, false);
+#undef LUCID_LAUNCH
 }
 #endif  // LUCID_BODY_ONLY
 
