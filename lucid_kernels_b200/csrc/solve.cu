@@ -24,18 +24,22 @@
 // Pair mode (few chains, where the hand-over latency between consecutive row-blocks is what limits a
 // chain): the grid is launched as clusters of two CTAs, work items are pairs of consecutive row-blocks of
 // a chain taken in a fixed rotation by the clusters, CTA 0 of a cluster solves the first row-block and
-// CTA 1 the second.  CTA 0 hands its result to CTA 1 directly: its epilogue threads write the tile into
-// the ring stages CTA 1 has claimed for it (st.shared::cluster) and one thread arrives on CTA 1's
-// barriers, which replaces "TMA store, release the flag, acquire it, TMA load" for every second
-// hand-over of the chain.  CTA 0 still stores and publishes the tile for all later row-blocks.
+// CTA 1 the second.  CTA 0 hands its result to CTA 1 directly: CTA 1 claims the two ring stages of its
+// last tile, arms their barriers with the byte count and bumps a counter in CTA 0's shared memory; CTA 0
+// stages the tile as always and one thread copies it into those stages with four bulk shared-to-shared
+// copies (no multicast), whose arrival completes CTA 1's stage barriers like a TMA load.  That replaces
+// "TMA store, release the flag, acquire it, TMA load" for every second hand-over of the chain.  CTA 0
+// still stores and publishes the tile for all later row-blocks; CTA 1 acknowledges receipt on the barrier
+// that guards CTA 0's staging buffer.
 //
-// Warp roles (384 threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 issues the
+// Warp roles (128 + 128 * kG threads): warp 0 K-producer (tickets, K_i, K_j half-tiles, X_i), warp 1 issues the
 // S products and owns TMEM, warp 2 Y-producer (rhs tile, flag waits, Y_j half-tiles), warp 3 issues the
-// P*Y and diagonal products, warps 4-7 / 8-11 two exp groups that split every tile's columns (64 each)
-// and share the epilogue the same way.  Two issuing warps because tcgen05.mma issue is nearly synchronous
+// P*Y and diagonal products, then kG exp groups of four warps (kG = 4 in the stand-alone kernels, 2 when the
+// program shares a launch with the dK program) that split every tile's columns (128 / kG each) and share
+// the epilogue the same way.  Two issuing warps because tcgen05.mma issue is nearly synchronous
 // with execution (the queue holds only a few instructions): the waits of one overlap the MMAs of the other.
 //
-// TMEM: three S buffers (tile g uses buffer g % 3) and the accumulator.  An exp thread streams its 64
+// TMEM: three S buffers (tile g uses buffer g % 3) and the accumulator.  An exp thread streams its
 // columns of S through registers in 16-column chunks (the next chunk's load in flight) and writes the
 // packed P chunk over S columns it has already consumed, so P needs no buffer of its own and the S
 // products run up to three tiles ahead of the P*Y products; a buffer returns to the S issuer when the

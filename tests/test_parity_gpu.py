@@ -191,6 +191,30 @@ def test_backward_in_one_launch_matches_separate_launches(ops, dtype, H):
     assert bool(torch.isfinite(dk0.float()).all())
 
 
+def test_pair_mode_matches_single_row_blocks(ops):
+    """With few chains the stand-alone solve kernels run as clusters of two CTAs that solve pairs of
+    row-blocks and hand the first result to the second through shared memory.  Same arithmetic in the same
+    order as single row-blocks: bit-identical, forward and reverse, bf16 and fp16."""
+    from lucid_kernels_b200 import _cabi
+
+    lib = _cabi.load()
+    for dtype, (B, N, H) in ((torch.bfloat16, (1, 8192, 8)), (torch.float16, (1, 4096, 3)), (torch.bfloat16, (2, 256, 1))):
+        K, V, G = orc.make_inputs(B, N, H, dtype=dtype, seed=31)
+        Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+        try:
+            lib.lucid_set_pair_solve(0)
+            lib.lucid_set_fused_backward(0, 0)
+            vp0 = ops._forward_sub_fwd(Kc, Vc, check=True)
+            dv0 = ops._forward_sub_bwd_dv(Kc, Gc, check=True)
+            lib.lucid_set_pair_solve(8)
+            vp1 = ops._forward_sub_fwd(Kc, Vc, check=True)
+            dv1 = ops._forward_sub_bwd_dv(Kc, Gc, check=True)
+        finally:
+            lib.lucid_set_pair_solve(8)
+            lib.lucid_set_fused_backward(2, 0)
+        assert torch.equal(vp0, vp1) and torch.equal(dv0, dv1), (dtype, B, N, H)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_key_scale_folded_into_the_kernels(ops, dtype):
     """k_scale: the operator acts on k_scale * k while the kernels read k itself.  Checked against the fp64
