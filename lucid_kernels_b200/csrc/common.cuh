@@ -79,26 +79,6 @@ __device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, vol
   return true;
 }
 
-// The same wait for a barrier that the peer CTA of a cluster arrives on (cluster-scope acquire).
-__device__ __forceinline__ bool wait_barrier_cluster(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
-                                                     Control* ctl, unsigned long long limit_ns, int chain, int row,
-                                                     int bar_id) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++spins & 255u) == 0) {
-      if (*cta_abort) return false;
-      if (globaltimer_ns() - t0 > limit_ns) {
-        *cta_abort = 1;
-        report_error(ctl, kErrBarrierTimeout, chain, row, 0, bar_id);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
 // A row-block is complete when its flag reaches kFlagComplete: set at once by the thread that stored the
 // block with TMA, or reached by the storing warps (8 or 16 of them) each adding their share with release
 // semantics after their own plain stores.

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the LUCID kernels use:
-// mbarrier, TMA tiled loads (no cluster multicast anywhere), tcgen05 MMA / TMEM, proxy fences,
+// mbarrier, TMA tiled loads (every load has a single destination CTA), tcgen05 MMA / TMEM, proxy fences,
 // and release/acquire flag accesses.  Everything here is device-only and header-only.
 #pragma once
 #include <cuda.h>
@@ -69,7 +69,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// thread-block clusters: the peer CTA's shared memory and barriers (no multicast loads anywhere)
+// thread-block clusters: the peer CTA's shared memory and barriers
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -82,35 +82,11 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t cta_r
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
   return r;
 }
-__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint4 v) {
-  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
 // arrive on a barrier of the peer CTA; releases this thread's earlier writes at cluster scope
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// arrive on a barrier of this CTA with a cluster-scope release (its waiter may be signalled on to the peer)
-__device__ __forceinline__ void mbar_arrive_rel_cluster(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// poll a barrier of this CTA that the peer CTA (or a thread relaying the peer's data) arrives on; the
-// non-blocking test, because a suspended try_wait was not woken promptly by arrivals from the other SM
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// bulk copy from this CTA's shared memory into the peer's (no multicast); completion is counted in bytes on
+// bulk copy from this CTA's shared memory into the peer's (one destination); completion is counted in bytes on
 // a barrier of the peer, like a TMA load there.  All addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_local_addr, uint32_t bytes,
                                                   uint32_t bar_cluster_addr) {
@@ -140,10 +116,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma operands)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-// the same for writes into the shared memory of any CTA of the cluster
-__device__ __forceinline__ void fence_proxy_async_cluster_smem() {
-  asm volatile("fence.proxy.async.shared::cluster;" ::: "memory");
 }
 // generic <-> async proxy ordering for global memory (flag acquire, then TMA load of the tile)
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }

@@ -27,7 +27,7 @@
 // CTA 1 the second.  CTA 0 hands its result to CTA 1 directly: CTA 1 claims the two ring stages of its
 // last tile, arms their barriers with the byte count and bumps a counter in CTA 0's shared memory; CTA 0
 // stages the tile as always and one thread copies it into those stages with four bulk shared-to-shared
-// copies (no multicast), whose arrival completes CTA 1's stage barriers like a TMA load.  That replaces
+// copies (each with one destination), whose arrival completes CTA 1's stage barriers like a TMA load.  That replaces
 // "TMA store, release the flag, acquire it, TMA load" for every second hand-over of the chain.  CTA 0
 // still stores and publishes the tile for all later row-blocks; CTA 1 acknowledges receipt on the barrier
 // that guards CTA 0's staging buffer.
