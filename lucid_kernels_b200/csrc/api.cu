@@ -193,6 +193,11 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
       pgrid = 2 * (items < sms / 2 ? items : sms / 2);
     }
     e = launch_solve(bf16, reverse, pair, tm_k, tm_in, tm_out, tm_x, tm_st, sa, pair ? pgrid : grid, stream);
+    if (pair && e != cudaSuccess) {
+      // no room for clusters on this device (a partitioned GPU, for instance): single row-blocks always launch
+      (void)cudaGetLastError();
+      e = launch_solve(bf16, reverse, false, tm_k, tm_in, tm_out, tm_x, tm_st, sa, grid, stream);
+    }
   }
   if (e != cudaSuccess) return (int)e;
   record_event(2, stream);
