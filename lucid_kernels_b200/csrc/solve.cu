@@ -713,26 +713,6 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           st0 = u_last & 3;
           st1 = (u_last + 1) & 3;
           u_peer = u_last + 2;
-          // a counter, not a barrier phase: the peer's producer may run an item ahead.  One lane per warp
-          // polls (cluster-scope acquire loads are expensive), the warp barrier passes the result on.
-          int ok = 1;
-          if (lane == 0 && ld_acquire_cluster_local(&s.peer_items) <= it) {
-            const uint64_t t0 = globaltimer_ns();
-            uint32_t spins = 0;
-            while (ld_acquire_cluster_local(&s.peer_items) <= it) {
-              if ((++spins & 63u) == 0) {
-                if (*cta_abort) { ok = 0; break; }
-                if (globaltimer_ns() - t0 > limit) {
-                  *cta_abort = 1;
-                  report_error(ctl, kErrBarrierTimeout, chain, i, 0, BAR_PEER_READY);
-                  ok = 0;
-                  break;
-                }
-              }
-            }
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) break;
         }
 #pragma unroll
         for (int c = 0; c < kVec; ++c) {
@@ -750,6 +730,26 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         if (tid == 128) {
           if (hand_over) {
             if (!wait_barrier(&s.stage_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_STAGE_FULL)) break;
+            // Has the peer claimed its stages for this item?  A counter, not a barrier phase: the peer's
+            // producer may run an item ahead.  Only this thread needs to know (cluster-scope acquire loads
+            // are expensive), and normally the answer has been yes for a while.
+            if (ld_acquire_cluster_local(&s.peer_items) <= it) {
+              const uint64_t t0 = globaltimer_ns();
+              uint32_t spins = 0;
+              bool ok = true;
+              while (ld_acquire_cluster_local(&s.peer_items) <= it) {
+                if ((++spins & 63u) == 0) {
+                  if (*cta_abort) { ok = false; break; }
+                  if (globaltimer_ns() - t0 > limit) {
+                    *cta_abort = 1;
+                    report_error(ctl, kErrBarrierTimeout, chain, i, 0, BAR_PEER_READY);
+                    ok = false;
+                    break;
+                  }
+                }
+              }
+              if (!ok) break;
+            }
             // The staged tile (two 64-column panels of 128 rows) goes to the peer as four 8 KiB bulk copies:
             // rows 0-63 of both panels into stage st0, rows 64-127 into st1 - the layout of a ring stage, and
             // the swizzle pattern repeats every 8 rows, so the bytes are copied as they are.  Their arrival
