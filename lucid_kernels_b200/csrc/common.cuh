@@ -147,9 +147,12 @@ constexpr int kTraceMax = 8192;
 #ifndef LUCID_TRACE_ROLES
 #define LUCID_TRACE_ROLES 0xffffffffu       // bit r: role r is traced
 #endif
+#ifndef LUCID_TRACE_BLOCK
+#define LUCID_TRACE_BLOCK 0                 // the CTA that is traced
+#endif
 #define LUCID_TR(buf, role, cnt, tag, q)                                              \
   do {                                                                                \
-    if ((((LUCID_TRACE_ROLES) >> (role)) & 1u) && (buf) != nullptr && blockIdx.x == 0 && (cnt) < kTraceMax) { \
+    if ((((LUCID_TRACE_ROLES) >> (role)) & 1u) && (buf) != nullptr && blockIdx.x == (LUCID_TRACE_BLOCK) && (cnt) < kTraceMax) { \
       long long* e_ = (buf) + ((long long)(role) * kTraceMax + (cnt)) * 3;            \
       e_[0] = (tag);                                                                  \
       e_[1] = (q);                                                                    \
