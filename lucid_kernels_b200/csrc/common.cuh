@@ -148,12 +148,16 @@ constexpr int kTraceMax = 8192;
 #define LUCID_TRACE_ROLES 0xffffffffu       // bit r: role r is traced
 #endif
 #ifndef LUCID_TRACE_BLOCK
-#define LUCID_TRACE_BLOCK 0                 // the CTA that is traced
+#define LUCID_TRACE_BLOCK 0                 // the first CTA that is traced
+#endif
+#ifndef LUCID_TRACE_NBLOCKS
+#define LUCID_TRACE_NBLOCKS 1               // how many consecutive CTAs are traced (8 role slots each)
 #endif
 #define LUCID_TR(buf, role, cnt, tag, q)                                              \
   do {                                                                                \
-    if ((((LUCID_TRACE_ROLES) >> (role)) & 1u) && (buf) != nullptr && blockIdx.x == (LUCID_TRACE_BLOCK) && (cnt) < kTraceMax) { \
-      long long* e_ = (buf) + ((long long)(role) * kTraceMax + (cnt)) * 3;            \
+    const unsigned tb_ = blockIdx.x - (LUCID_TRACE_BLOCK);                            \
+    if ((((LUCID_TRACE_ROLES) >> (role)) & 1u) && (buf) != nullptr && tb_ < (LUCID_TRACE_NBLOCKS) && (cnt) < kTraceMax) { \
+      long long* e_ = (buf) + ((long long)((role) + 8 * tb_) * kTraceMax + (cnt)) * 3; \
       e_[0] = (tag);                                                                  \
       e_[1] = (q);                                                                    \
       e_[2] = clock64();                                                              \
