@@ -297,7 +297,7 @@ def main():
     ms_total = ev0.elapsed_time(ev1)
     # The SM clock as the kernels see it: one instrumented forward straight after the timed region (GPU
     # still at its loaded power state) records wall time and SM cycles per row-block; nvidia-smi's
-    # instantaneous readings at 100 ms intervals catch idle moments of a sub-second region and read high.
+    # instantaneous readings at 50 ms intervals catch idle moments of a sub-second region and read high.
     try:
         _, ts = _forward_sub_fwd(sets[0][0], sets[0][1], use_diag_solve=True, instrument=True)
         torch.cuda.synchronize()
