@@ -143,6 +143,12 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
  * whose grid is one CTA per row-block in launch order (tile_scheduler.py:105-117). */
 void lucid_set_head_steps(int steps);
 
+/* Scheduler knob: the first `steps` row-blocks of every group of systems but the first are dealt out
+ * alternately with the last `steps` row-blocks of the group before, so that the short, latency-bound start of a
+ * group runs beside long row-blocks that keep the other SMs busy (< 0 = default).  No counterpart in the
+ * reference, whose grid is one CTA per row-block. */
+void lucid_set_group_overlap(int steps);
+
 /* Combined backward (mode LUCID_BWD_COMBINED): with at most `max_chains` (batch, head) systems the reverse
  * solve, then bound by its chain latency, and the dK program run in ONE launch - `solve_ctas` CTAs solve,
  * the others compute dK row-blocks as the solve publishes them and are joined by the solving CTAs at the

@@ -174,9 +174,9 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     if (kPair) {
       // a work item is a pair of consecutive row-blocks (T is even): this CTA solves the first or second
       int ps;
-      if (!decode_ticket(ticket, P.C, T >> 1, P.group, 0, chain, ps)) return false;
+      if (!decode_ticket(ticket, P.C, T >> 1, P.group, 0, 0, chain, ps)) return false;
       step = 2 * ps + (int)crank;
-    } else if (!decode_ticket(ticket, P.C, T, P.group, P.head, chain, step)) {
+    } else if (!decode_ticket(ticket, P.C, T, P.group, P.head, P.overlap, chain, step)) {
       return false;
     }
     if (kReverse) {

@@ -215,6 +215,30 @@ def test_pair_mode_matches_single_row_blocks(ops):
         assert torch.equal(vp0, vp1) and torch.equal(dv0, dv1), (dtype, B, N, H)
 
 
+def test_group_overlap_only_reorders_the_work(ops):
+    """Scheduler knob: the start of a group of chains dealt out alternately with the end of the group before.
+    Every row-block is still solved by one CTA from the same inputs: bit-identical results, forward and
+    reverse, for an overlap shorter than, equal to and (clamped) longer than half the row-blocks."""
+    from lucid_kernels_b200 import _cabi
+
+    lib = _cabi.load()
+    K, V, G = orc.make_inputs(2, 2048, 3, dtype=torch.bfloat16, seed=37)
+    Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+    try:
+        lib.lucid_set_pair_solve(0)
+        lib.lucid_set_group_overlap(0)
+        vp0 = ops._forward_sub_fwd(Kc, Vc, check=True, chain_group=2)
+        dv0 = ops._forward_sub_bwd_dv(Kc, Gc, check=True, chain_group=2)
+        for steps in (3, 8, 100):
+            lib.lucid_set_group_overlap(steps)
+            vp1 = ops._forward_sub_fwd(Kc, Vc, check=True, chain_group=2)
+            dv1 = ops._forward_sub_bwd_dv(Kc, Gc, check=True, chain_group=2)
+            assert torch.equal(vp0, vp1) and torch.equal(dv0, dv1), steps
+    finally:
+        lib.lucid_set_pair_solve(8)
+        lib.lucid_set_group_overlap(-1)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_key_scale_folded_into_the_kernels(ops, dtype):
     """k_scale: the operator acts on k_scale * k while the kernels read k itself.  Checked against the fp64
