@@ -89,6 +89,11 @@ def load() -> ctypes.CDLL:
         lib.lucid_set_head_steps.argtypes = [c.c_int]
         lib.lucid_set_group_overlap.restype = None
         lib.lucid_set_group_overlap.argtypes = [c.c_int]
+        # LUCID_B200_GROUP_OVERLAP / LUCID_B200_HEAD_STEPS: the scheduler's experiment knobs (steps)
+        if os.environ.get("LUCID_B200_GROUP_OVERLAP"):
+            lib.lucid_set_group_overlap(int(os.environ["LUCID_B200_GROUP_OVERLAP"]))
+        if os.environ.get("LUCID_B200_HEAD_STEPS"):
+            lib.lucid_set_head_steps(int(os.environ["LUCID_B200_HEAD_STEPS"]))
         lib.lucid_set_pair_solve.restype = None
         lib.lucid_set_pair_solve.argtypes = [c.c_int]
         if os.environ.get("LUCID_B200_PAIR_SOLVE"):
