@@ -54,7 +54,9 @@ extern "C" {
 
 /* Bytes of scratch the calls below need for a (B, N, H, 128) problem.  The workspace holds the
  * inter-block flags, the scheduler's control words, the per-block unit-triangular inverses
- * (B*H*N*128 16-bit values) and their row scales.  Replaces the per-call torch.zeros / torch.empty
+ * (B*H*N*128 16-bit values) and their row scales, and for B*H <= 2 the fp32 partial sums of dK that the
+ * one-launch backward exchanges between work items (64 KiB per 128 rows; a call given less than this, but
+ * enough for the rest, runs without them).  Replaces the per-call torch.zeros / torch.empty
  * allocations of forward_sub_interface.py:97-103,217-219,297-300 and the diag_inv tensor of :109-117. */
 size_t lucid_workspace_bytes(int B, int N, int H);
 
@@ -148,6 +150,11 @@ void lucid_set_head_steps(int steps);
  * group runs beside long row-blocks that keep the other SMs busy (< 0 = default).  No counterpart in the
  * reference, whose grid is one CTA per row-block. */
 void lucid_set_group_overlap(int steps);
+
+/* One-launch backward (see lucid_set_fused_backward) with one or two systems: a row-block's dK tiles are dealt
+ * out as two work items whose fp32 sums meet through the workspace, so that the launch ends in units of half a
+ * row-block (on = 1, default) instead of a whole one (on = 0).  No counterpart in the reference. */
+void lucid_set_dk_split(int on);
 
 /* Combined backward (mode LUCID_BWD_COMBINED): with at most `max_chains` (batch, head) systems the reverse
  * solve, then bound by its chain latency, and the dK program run in ONE launch - `solve_ctas` CTAs solve,

@@ -28,7 +28,7 @@ _I64x3 = ctypes.c_int64 * 3
 
 EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_read_status",
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
-           "lucid_profile_next_call", "lucid_set_head_steps", "lucid_set_group_overlap", "lucid_fwd_sub_static",
+           "lucid_profile_next_call", "lucid_set_head_steps", "lucid_set_group_overlap", "lucid_set_dk_split", "lucid_fwd_sub_static",
            "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled",
            "lucid_set_pair_solve")
 
@@ -89,6 +89,8 @@ def load() -> ctypes.CDLL:
         lib.lucid_set_head_steps.argtypes = [c.c_int]
         lib.lucid_set_group_overlap.restype = None
         lib.lucid_set_group_overlap.argtypes = [c.c_int]
+        lib.lucid_set_dk_split.restype = None
+        lib.lucid_set_dk_split.argtypes = [c.c_int]
         # LUCID_B200_GROUP_OVERLAP / LUCID_B200_HEAD_STEPS: the scheduler's experiment knobs (steps)
         if os.environ.get("LUCID_B200_GROUP_OVERLAP"):
             lib.lucid_set_group_overlap(int(os.environ["LUCID_B200_GROUP_OVERLAP"]))

@@ -17,6 +17,7 @@ static int g_fuse_solve_ctas = 0;   // 0 = automatic share
 static int g_pair_max_chains = 8;   // solve pairs of row-blocks with clusters of two CTAs up to this many chains
 static int g_head = -1;   // scheduler knob; < 0 = default
 static int g_overlap = -1;   // scheduler knob; < 0 = default
+static int g_dk_split = 1;   // one-launch backward: dK row-blocks as two work items
 static inline void record_event(int i, cudaStream_t stream) {
   if (g_events[i]) cudaEventRecord(g_events[i], stream);
 }
@@ -28,17 +29,23 @@ static inline void record_event(int i, cudaStream_t stream) {
 //   lam_inv             C*T*128 fp32
 //   timestamps          C*T*8 int64
 struct Layout {
-  size_t flags, x, lam, ts, total;
+  size_t flags, dksync, x, lam, ts, partial, need, total;   // need: without the dK partial sums
 };
+// dK work items split in two are used with at most this many chains (the fp32 sums of the half that finishes
+// first go through the workspace: 64 KiB per row-block)
+constexpr int kSplitMaxChains = 2;
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static Layout make_layout(int B, int N, int H) {
   const size_t CT = (size_t)B * H * (N / kBlock);
   Layout l;
   l.flags = 256;
-  l.x = align_up(l.flags + CT * 4, 1024);
+  l.dksync = l.flags + CT * 4;                         // claim counters and completion flags, zeroed with the flags
+  l.x = align_up(l.dksync + CT * 8, 1024);
   l.lam = l.x + CT * kTileBytes;
   l.ts = align_up(l.lam + CT * kBlock * 4, 256);
-  l.total = l.ts + CT * 8 * 8;
+  l.need = l.ts + CT * 8 * 8;
+  l.partial = align_up(l.need, 1024);
+  l.total = l.partial + ((size_t)B * H <= kSplitMaxChains ? CT * (size_t)kBlock * kBlock * 4 : 0);
   return l;
 }
 
@@ -233,6 +240,8 @@ void lucid_set_head_steps(int steps) { g_head = steps; }
 
 void lucid_set_group_overlap(int steps) { g_overlap = steps; }
 
+void lucid_set_dk_split(int on) { g_dk_split = on; }
+
 void lucid_set_pair_solve(int max_chains) { g_pair_max_chains = max_chains; }
 
 void lucid_set_fused_backward(int max_chains, int solve_ctas) {
@@ -272,7 +281,7 @@ int lucid_fwd_sub_scaled(const void* k, const void* v, void* v_prime, const int6
   if (!workspace) return LUCID_E_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) % 1024) return LUCID_E_BAD_ALIGNMENT;
   const Layout lay = make_layout(B, N, H);
-  if (workspace_bytes < lay.total) return LUCID_E_WORKSPACE_TOO_SMALL;
+  if (workspace_bytes < lay.need) return LUCID_E_WORKSPACE_TOO_SMALL;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);   // control words + flags
@@ -312,7 +321,7 @@ int lucid_fwd_sub_static(const void* k, const void* v, void* v_prime, const int6
   uintptr_t base = reinterpret_cast<uintptr_t>(g_static_scratch_ptr[dev]);
   const uintptr_t aligned = (base + 1023) & ~uintptr_t(1023);
   const size_t usable = LUCID_STATIC_SCRATCH_BYTES - (aligned - base);
-  const size_t need = make_layout(B, N, H).total;
+  const size_t need = make_layout(B, N, H).need;
   if (need > usable) return LUCID_E_STATIC_SCRATCH_TOO_SMALL;
   // the array still holds whatever the previous call left: never trust a cached inverse in it
   flags &= ~LUCID_FLAG_REUSE_DIAG;
@@ -350,7 +359,7 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
   if (!workspace) return LUCID_E_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) % 1024) return LUCID_E_BAD_ALIGNMENT;
   const Layout lay = make_layout(B, N, H);
-  if (workspace_bytes < lay.total) return LUCID_E_WORKSPACE_TOO_SMALL;
+  if (workspace_bytes < lay.need) return LUCID_E_WORKSPACE_TOO_SMALL;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);
@@ -372,6 +381,9 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
     fd.args.follow_flags = nullptr;
     fd.args.follow_ctl = nullptr;
     fd.args.trace = g_trace;
+    fd.args.split = 0;
+    fd.args.partial = reinterpret_cast<float*>(ws + lay.partial);
+    fd.args.sync = reinterpret_cast<int*>(ws + lay.dksync);
     fd.args.p = p;
   }
   // With one or two chains the reverse solve is bound by its chain latency and leaves SMs idle: the dK
@@ -385,6 +397,9 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
   const bool fuse = mode == LUCID_BWD_COMBINED && p.C <= g_fuse_max_chains && !p.instrument && !p.no_sync &&
                     CT >= 2 * sms && n_solve >= 1;
   fd.n_solve = n_solve;
+  // In that launch a row-block of dK (0.31 ms at N=32768) is the unit in which the launch ends; two half items
+  // per row-block halve it.
+  if (fuse && g_dk_split && p.C <= kSplitMaxChains && workspace_bytes >= lay.total) fd.args.split = 1;
   rc = run_solve(true, k, dv_prime, dv, k_strides, dvp_strides, dv_strides, p, bf16, ws, lay, stream,
                  fuse ? &fd : nullptr);
   cudaEvent_t ev_dk = g_events[3];

@@ -40,6 +40,7 @@ struct DkSmem {
   int tk_slot[2];
   uint32_t tmem_base;
   int abort_flag;
+  int claim;       // split items: 0 = this CTA finished its half of the row-block first, 1 = second
 };
 
 enum DkBar : int {
@@ -113,7 +114,11 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
 
   // Tile q of row-block i (n tiles): the lower part j = 0..i-1, [D1, D2 at j = i], the upper part.
   //   n_low = i (+1 with D1); tiles q < n_low are "lower" (A = dV_i, Z = V'_j).
-  auto item_geometry = [&](int ticket, int& chain, int& i, int& n, int& n_low) -> bool {
+  // With args.split a row-block's tiles are dealt out as two work items, tiles [q0, q1) each; the item that
+  // finishes second adds the other's partial sums (see the epilogue).
+  auto item_geometry = [&](int ticket, int& chain, int& i, int& n_low, int& q0, int& q1) -> bool {
+    const int half = args.split ? (ticket & 1) : 0;
+    if (args.split) ticket >>= 1;
     if (ticket >= P.C * T) return false;
     if (args.follow_flags) {
       chain = ticket % P.C;
@@ -123,7 +128,13 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
       i = ticket % T;
     }
     n_low = i + (diag_tiles ? 1 : 0);
-    n = T - 1 + (diag_tiles ? 2 : 0);
+    const int n = T - 1 + (diag_tiles ? 2 : 0);
+    q0 = 0;
+    q1 = n;
+    if (args.split) {
+      if (half) q0 = n >> 1;
+      else q1 = n >> 1;
+    }
     return true;
   };
   auto tile_j = [&](int i, int n_low, int q) -> int {
@@ -146,8 +157,8 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
         const int ticket = atomicAdd(&ctl->ticket, 1);
         s.tk_slot[slot] = ticket;
         mbar_arrive(&s.tk_full[slot]);
-        int chain, i, n, n_low;
-        if (!item_geometry(ticket, chain, i, n, n_low)) break;
+        int chain, i, n_low, q0, q1;
+        if (!item_geometry(ticket, chain, i, n_low, q0, q1)) break;
         const int b = chain / H, h = chain % H;
         if (!wait_barrier(&s.ki_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_KI_FREE)) break;
         mbar_expect_tx(&s.ki_full, kTileBytes);
@@ -168,13 +179,13 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           ++swaps;
           return true;
         };
-        if (n_low > 0 && !load_a(&tm_dv)) break;
-        for (int q = 0; q < n && alive; ++q) {
-          if (q == n_low && n_low < n) {
+        if (q0 < q1 && !load_a(q0 < n_low ? &tm_dv : &tm_vp)) break;
+        for (int q = q0; q < q1 && alive; ++q) {
+          if (q == n_low && q0 < n_low) {
             if (!load_a(&tm_vp)) { alive = false; break; }
           }
           const int j = tile_j(i, n_low, q);
-          const uint32_t gq = g + q;
+          const uint32_t gq = g + (q - q0);
           const int ks = gq % 3, zs = gq & 1;
           if (!wait_barrier(&s.k_empty[ks], ((gq / 3) & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_K_EMPTY)) {
             alive = false;
@@ -192,7 +203,7 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           tma_load_4d(s.zring[zs], tz, &s.z_full[zs], 0, j * kBlock, h, b);
           tma_load_4d(s.zring[zs] + kHalfBytes, tz, &s.z_full[zs], 64, j * kBlock, h, b);
         }
-        g += n;
+        g += q1 - q0;
       }
     }
   } else if (warp == 1) {
@@ -215,16 +226,16 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
         const int ticket = s.tk_slot[slot];
         __syncwarp();
         mbar_arrive_w(&s.tk_empty[slot]);
-        int chain, i, n, n_low;
-        if (!item_geometry(ticket, chain, i, n, n_low)) break;
-        for (int q = 0; q < n; ++q) {
-          const uint32_t gq = g + q;
+        int chain, i, n_low, q0, q1;
+        if (!item_geometry(ticket, chain, i, n_low, q0, q1)) break;
+        for (int q = q0; q < q1; ++q) {
+          const uint32_t gq = g + (q - q0);
           // G(gq-1) is in the registers of all 256 threads: the single G buffer is free again
           if (gq > 0 &&
               !wait_barrier(&s.g_free, (gq - 1) & 1, cta_abort, ctl, limit, chain, i, DK_G_FREE)) { alive = false; break; }
           if (leader) LUCID_TR(args.trace, 2, trc, 34, gq);
           // the A buffer changes from dV_i to V'_i at q == n_low; wait for the load that serves tile q
-          if ((q == 0 && n_low > 0) || (q == n_low && n_low < n)) {
+          if (q == q0 || (q == n_low && q0 < n_low)) {
             if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) { alive = false; break; }
             ++swaps;
           }
@@ -242,10 +253,10 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           umma_commit_w(&s.g_full);
           if (leader) LUCID_TR(args.trace, 2, trc, 33, gq);
           // last lower tile (or last tile): the A buffer may be overwritten once this product is done
-          if (q == n_low - 1 || q == n - 1) umma_commit_w(&s.ai_free);
+          if ((q == n_low - 1 && q0 < n_low) || q == q1 - 1) umma_commit_w(&s.ai_free);
         }
         if (!alive) break;
-        g += n;
+        g += q1 - q0;
       }
     }
   } else if (warp == 2) {
@@ -268,13 +279,13 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
         const int ticket = s.tk_slot[slot];
         __syncwarp();
         mbar_arrive_w(&s.tk_empty[slot]);
-        int chain, i, n, n_low;
-        if (!item_geometry(ticket, chain, i, n, n_low)) break;
+        int chain, i, n_low, q0, q1;
+        if (!item_geometry(ticket, chain, i, n_low, q0, q1)) break;
         if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, DK_KI_FULL)) break;
         tc_fence_after_sync();
-        if (leader) LUCID_TR(args.trace, 1, trc, 35, n);
-        for (int q = 0; q < n; ++q) {
-          const uint32_t gq = g + q;
+        if (leader) LUCID_TR(args.trace, 1, trc, 35, q1 - q0);
+        for (int q = q0; q < q1; ++q) {
+          const uint32_t gq = g + (q - q0);
           const uint32_t ks = gq % 3;
           const uint32_t buf = gq & 1;
           // W of two tiles ago lived in this buffer: its W*K_j product must have completed
@@ -297,9 +308,9 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           if (leader) LUCID_TR(args.trace, 1, trc, 31, gq);
         }
         if (!alive) break;
-        g += n;
+        g += q1 - q0;
         // K_i may be replaced once the S products of this item are complete
-        if (n > 0) umma_commit_w(&s.ki_free);
+        if (q1 > q0) umma_commit_w(&s.ki_free);
         else mbar_arrive_w(&s.ki_free);
       }
     }
@@ -321,16 +332,16 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
         const int ticket = s.tk_slot[slot];
         __syncwarp();
         mbar_arrive_w(&s.tk_empty[slot]);
-        int chain, i, n, n_low;
-        if (!item_geometry(ticket, chain, i, n, n_low)) break;
-        for (int q = 0; q < n; ++q) {
-          const uint32_t gq = g + q;
+        int chain, i, n_low, q0, q1;
+        if (!item_geometry(ticket, chain, i, n_low, q0, q1)) break;
+        for (int q = q0; q < q1; ++q) {
+          const uint32_t gq = g + (q - q0);
           // per-buffer barrier: the exp groups may be one tile ahead of this warp, never two on one buffer
           if (!wait_barrier(&s.w_ready[gq & 1], (gq >> 1) & 1, cta_abort, ctl, limit, chain, i, DK_W_READY)) {
             alive = false;
             break;
           }
-          if (q == 0 &&
+          if (q == q0 &&
               !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_ACC_FREE)) {
             alive = false;
             break;
@@ -345,16 +356,16 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           for (int k = 0; k < 8; ++k) {
             // W columns: k-steps 0-3 packed at columns 0-31, k-steps 4-7 at columns 64-95 of the S buffer
             const uint32_t a_col = (k < 4) ? k * 8 : 64 + (k - 4) * 8;
-            umma_ts_w(tmem + kDkAcc, w_tmem + a_col, db + k * (2048 >> 4), idesc_wk, (q | k) ? 1u : 0u);
+            umma_ts_w(tmem + kDkAcc, w_tmem + a_col, db + k * (2048 >> 4), idesc_wk, ((q - q0) | k) ? 1u : 0u);
           }
           umma_commit_w(&s.k_empty[ks]);
           umma_commit_w(&s.sbuf_free[buf]);
           if (leader) LUCID_TR(args.trace, 5, trc, 51, gq);
         }
         if (!alive) break;
-        g += n;
+        g += q1 - q0;
         // an item without tiles must not run ahead of the epilogue that still owns the previous phase
-        if (n == 0 && !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_ACC_FREE)) break;
+        if (q1 == q0 && !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_ACC_FREE)) break;
         umma_commit_w(&s.acc_full);
       }
     }
@@ -376,11 +387,11 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
       const int ticket = s.tk_slot[slot];
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.tk_empty[slot]);
-      int chain, i, n, n_low;
-      if (!item_geometry(ticket, chain, i, n, n_low)) break;
+      int chain, i, n_low, q0, q1;
+      if (!item_geometry(ticket, chain, i, n_low, q0, q1)) break;
       const int b = chain / H, h = chain % H;
-      for (int q = 0; q < n; ++q) {
-        const uint32_t gq = g + q;
+      for (int q = q0; q < q1; ++q) {
+        const uint32_t gq = g + (q - q0);
         const uint32_t s_tmem = lane_base + ((gq & 1) ? kDkS1 : kDkS0) + wg * 64;
         const uint32_t g_tmem = lane_base + kDkG + wg * 64;
         if (!wait_barrier(&s.g_full, gq & 1, cta_abort, ctl, limit, chain, i, DK_G_FULL)) {
@@ -442,7 +453,7 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
         if (tr_lead) LUCID_TR(args.trace, 3 + wg, trc, 43, gq);
       }
       if (!alive) break;
-      g += n;
+      g += q1 - q0;
 
       // ---- epilogue: dK_i columns 64*wg .. +63 ----
       if (!wait_barrier(&s.acc_full, it & 1, cta_abort, ctl, limit, chain, i, DK_ACC_FULL)) break;
@@ -450,15 +461,49 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
       typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
       elem_t* out_row = reinterpret_cast<elem_t*>(args.dk) + (long long)b * args.dk_strides.b +
                         (long long)(i * kBlock + row) * args.dk_strides.n + (long long)h * args.dk_strides.h + wg * 64;
+      // Split items: whichever half of the row-block finishes first leaves its fp32 sums in the workspace and
+      // sets a flag; the other half waits for that flag (bounded; the first half is already in its epilogue
+      // when the second learns that it is second), adds the sums and writes dK_i.
+      int order = -1;
+      float* part_row = nullptr;
+      const int rb = chain * T + i;
+      if (args.split) {
+        part_row = args.partial + ((long long)rb * kBlock + row) * kBlock + wg * 64;
+        if (tid == 128) s.claim = atomicAdd(args.sync + rb, 1);
+        named_bar_sync(1, 256);
+        order = s.claim;
+        if (order == 1) {
+          if (tid == 128 && !wait_flag(args.sync + P.C * T + rb, cta_abort, ctl, limit, chain, i, i, nullptr))
+            *cta_abort = 1;
+          named_bar_sync(1, 256);
+          if (*cta_abort) break;
+        }
+      }
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         uint32_t v[32];
-        if (n > 0) {
+        if (q1 > q0) {
           tmem_ld32(lane_base + kDkAcc + wg * 64 + cc * 32, v);
           tmem_wait_ld();
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = 0u;
+        }
+        if (order == 0) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(part_row + cc * 32 + c * 4) = make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+          continue;
+        }
+        if (order == 1) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(part_row + cc * 32 + c * 4));
+            v[c * 4] = __float_as_uint(__uint_as_float(v[c * 4]) + o.x);
+            v[c * 4 + 1] = __float_as_uint(__uint_as_float(v[c * 4 + 1]) + o.y);
+            v[c * 4 + 2] = __float_as_uint(__uint_as_float(v[c * 4 + 2]) + o.z);
+            v[c * 4 + 3] = __float_as_uint(__uint_as_float(v[c * 4 + 3]) + o.w);
+          }
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -469,6 +514,12 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
                                 __uint_as_float(v[c * 8 + 2 * e + 1]) * P.out_scale);
           *reinterpret_cast<uint4*>(out_row + cc * 32 + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
         }
+      }
+      if (order == 0) {
+        // every thread's sums are ordered before the flag: fence, meet, then one release store
+        __threadfence();
+        named_bar_sync(1, 256);
+        if (tid == 128) st_release_gpu(args.sync + P.C * T + rb, kFlagComplete);
       }
       tc_fence_before_sync();
       mbar_arrive(&s.acc_free);

@@ -31,6 +31,9 @@ struct DkArgs {
   const int* follow_flags;  // (C, T) flags of the reverse solve running in the same launch, or null
   Control* follow_ctl;      // that solve's control block (its failure releases the flag waits)
   long long* trace;         // debugging builds only (LUCID_TRACE); null otherwise
+  int split;                // 1: a row-block's tiles are two work items whose sums meet through `partial`
+  float* partial;           // (C*T, 128, 128) fp32 sums of the half that finished first (split only)
+  int* sync;                // (2, C*T) zeroed: claim counters, then completion flags (split only)
   Problem p;
 };
 

@@ -35,7 +35,9 @@ def test_workspace_size_and_status_strings(lib):
     assert lib.lucid_workspace_bytes(1, 100, 1) == 0
     small = lib.lucid_workspace_bytes(1, 128, 1)
     big = lib.lucid_workspace_bytes(2, 32768, 8)
-    assert 32768 < small < 65536
+    # one tile of inverses plus the fp32 dK partial sums that one or two systems may use (64 KiB per row-block)
+    assert 32768 + 65536 < small < 65536 + 65536
+    assert lib.lucid_workspace_bytes(1, 128, 3) < 3 * 65536        # three systems: no partial sums
     assert 128 * 2 ** 20 < big < 140 * 2 ** 20
     assert lib.lucid_status_string(0) == b"ok"
     assert b"128" in lib.lucid_status_string(-1)

@@ -172,7 +172,9 @@ def test_large_sizes_by_properties(ops):
 @pytest.mark.parametrize("dtype,H", [(torch.bfloat16, 2), (torch.float16, 1)])
 def test_backward_in_one_launch_matches_separate_launches(ops, dtype, H):
     """With one or two systems per GPU the combined backward runs the reverse solve and the dK program in one
-    launch (the dK CTAs follow the solve's flags).  Same arithmetic in the same order: bit-identical."""
+    launch (the dK CTAs follow the solve's flags).  With whole row-blocks as dK work items: same arithmetic in
+    the same order, bit-identical.  With a row-block's tiles dealt out as two items (the default there) the two
+    fp32 partial sums are added at the end instead of one running sum: dV bit-identical, dK equal to rounding."""
     from lucid_kernels_b200 import _cabi
 
     lib = _cabi.load()
@@ -184,10 +186,17 @@ def test_backward_in_one_launch_matches_separate_launches(ops, dtype, H):
         dv0, dk0 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
         for solve_ctas in (0, 20, 120):                         # automatic share, a small and a large one
             lib.lucid_set_fused_backward(2, solve_ctas)
+            lib.lucid_set_dk_split(0)
             dv1, dk1 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
             assert torch.equal(dv0, dv1) and torch.equal(dk0, dk1), solve_ctas
+            lib.lucid_set_dk_split(1)
+            dv2, dk2 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+            assert torch.equal(dv0, dv2), solve_ctas
+            rel = float((dk2.float() - dk0.float()).norm() / dk0.float().norm())
+            assert rel < 1e-3, (solve_ctas, rel)                # bf16/fp16 rounding of a differently ordered sum
     finally:
-        lib.lucid_set_fused_backward(2, 0)                      # library default
+        lib.lucid_set_fused_backward(2, 0)                      # library defaults
+        lib.lucid_set_dk_split(1)
     assert bool(torch.isfinite(dk0.float()).all())
 
 
