@@ -21,6 +21,10 @@
 // 16-column chunks (the next chunk's TMEM load in flight under the current chunk's arithmetic), forming
 // w = -exp(s) * g in one pass, and writes the packed chunk over S columns it has already consumed.
 // S(q+1) reuses the buffer W(q-1) sat in and is issued as soon as that product has completed.
+//
+// Work items: a whole row-block, or (args.split, used by the one-launch backward with one or two chains,
+// where the launch would otherwise end in units of a whole row-block) half of its tiles; the two halves
+// meet in the epilogue through fp32 sums in the workspace.
 #include <type_traits>
 #include "kernels.h"
 
