@@ -23,7 +23,6 @@ reference's own functions (tests/golden/make_golden.py extracts and executes the
 """
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch
