@@ -131,3 +131,29 @@ def test_interface_mirrors_reference_signatures():
     assert list(sig.parameters)[:5] == ["k", "dv_prime", "block_size", "use_diag_solve", "instrument"]
     sig = inspect.signature(cute._forward_sub_bwd_combined)
     assert list(sig.parameters)[:6] == ["k", "v_prime", "dv_prime", "block_size", "use_diag_solve", "instrument"]
+
+
+def test_work_item_order_keeps_every_chain_in_step_order(tmp_path):
+    """The solve kernels' ticket order (csrc/schedule.h), compiled for the host: every (chain, step) exactly
+    once and each chain's steps in increasing order, for plain groups, a common head, overlapping groups,
+    ragged groups and the clamped cases - the property that makes the flag waits deadlock-free."""
+    import random
+    import shutil
+    import subprocess
+
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no host compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "ticket_order")
+    subprocess.run([gxx, "-O1", "-std=c++17", "-I", os.path.join(root, "lucid_kernels_b200", "csrc"), "-o", exe,
+                    os.path.join(root, "tests", "host", "ticket_order.cpp")], check=True)
+    cases = ["16,256,4,0,0", "16,256,4,0,96", "16,256,4,32,96", "16,256,4,200,28", "16,256,4,200,29",
+             "8,1024,1,0,512", "8,64,2,5,32", "6,10,2,3,3", "5,10,2,2,3", "6,10,3,10,3", "1,7,1,0,3", "3,1,2,0,1"]
+    rng = random.Random(0)
+    for _ in range(200):
+        C, T = rng.randint(1, 12), rng.randint(1, 40)
+        cases.append(f"{C},{T},{rng.randint(1, C)},{rng.randint(-1, T + 1)},{rng.randint(0, T)}")
+    out = subprocess.run([exe, *cases], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout
+    assert out.stdout.strip() == f"ok {len(cases)}"
