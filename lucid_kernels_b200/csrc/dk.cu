@@ -121,29 +121,7 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
   // With args.split a row-block's tiles are dealt out as two work items, tiles [q0, q1) each; the item that
   // finishes second adds the other's partial sums (see the epilogue).
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n_low, int& q0, int& q1) -> bool {
-    const int half = args.split ? (ticket & 1) : 0;
-    if (args.split) ticket >>= 1;
-    if (ticket >= P.C * T) return false;
-    if (args.follow_flags) {
-      chain = ticket % P.C;
-      i = T - 1 - ticket / P.C;
-    } else {
-      chain = ticket / T;
-      i = ticket % T;
-    }
-    n_low = i + (diag_tiles ? 1 : 0);
-    const int n = T - 1 + (diag_tiles ? 2 : 0);
-    q0 = 0;
-    q1 = n;
-    if (args.split) {
-      if (half) q0 = n >> 1;
-      else q1 = n >> 1;
-    }
-    return true;
-  };
-  auto tile_j = [&](int i, int n_low, int q) -> int {
-    if (q < n_low) return q;                       // 0..i-1, then i (D1)
-    return diag_tiles ? q - 1 : q + 1;             // i (D2), i+1.. | i+1..
+    return dk_item(ticket, P.C, T, args.follow_flags != nullptr, args.split != 0, diag_tiles, chain, i, n_low, q0, q1);
   };
 
   if (warp == 0) {
@@ -183,12 +161,12 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           ++swaps;
           return true;
         };
-        if (q0 < q1 && !load_a(q0 < n_low ? &tm_dv : &tm_vp)) break;
+        if (q0 < q1 && !load_a(dk_first_a_is_dv(q0, n_low) ? &tm_dv : &tm_vp)) break;
         for (int q = q0; q < q1 && alive; ++q) {
-          if (q == n_low && q0 < n_low) {
+          if (dk_reloads_a_at(q, q0, n_low)) {
             if (!load_a(&tm_vp)) { alive = false; break; }
           }
-          const int j = tile_j(i, n_low, q);
+          const int j = dk_tile_j(n_low, q, diag_tiles);
           const uint32_t gq = g + (q - q0);
           const int ks = gq % 3, zs = gq & 1;
           if (!wait_barrier(&s.k_empty[ks], ((gq / 3) & 1) ^ 1, cta_abort, ctl, limit, chain, i, DK_K_EMPTY)) {
@@ -239,7 +217,7 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
               !wait_barrier(&s.g_free, (gq - 1) & 1, cta_abort, ctl, limit, chain, i, DK_G_FREE)) { alive = false; break; }
           if (leader) LUCID_TR(args.trace, 2, trc, 34, gq);
           // the A buffer changes from dV_i to V'_i at q == n_low; wait for the load that serves tile q
-          if (q == q0 || (q == n_low && q0 < n_low)) {
+          if (dk_waits_a_at(q, q0, n_low)) {
             if (!wait_barrier(&s.ai_full, swaps & 1, cta_abort, ctl, limit, chain, i, DK_AI_FULL)) { alive = false; break; }
             ++swaps;
           }
@@ -257,7 +235,7 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           umma_commit_w(&s.g_full);
           if (leader) LUCID_TR(args.trace, 2, trc, 33, gq);
           // last lower tile (or last tile): the A buffer may be overwritten once this product is done
-          if ((q == n_low - 1 && q0 < n_low) || q == q1 - 1) umma_commit_w(&s.ai_free);
+          if (dk_frees_a_after(q, q0, q1, n_low)) umma_commit_w(&s.ai_free);
         }
         if (!alive) break;
         g += q1 - q0;

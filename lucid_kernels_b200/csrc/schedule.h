@@ -72,4 +72,49 @@ LUCID_HD bool decode_ticket(int t, int C, int T, int group, int head, int overla
   return true;
 }
 
+// ---------------------------------------------------------------------------------------------
+// dK work items.  Row-block i of a chain streams n = T - 1 (+ 2 with diagonal tiles) tiles: the lower part
+// j = 0 .. i-1 (A operand dV_i), with diagonal tiles D1 at j = i, then D2 at j = i (A operand V'_i from here
+// on) and the upper part j = i+1 .. T-1.  n_low = number of tiles that use dV_i.  An item covers tiles
+// [q0, q1): all of them, or with `split` one half each for two consecutive tickets.  In `follow` order the
+// row-blocks come last one first, step-major over the chains (the order in which the reverse solve of the
+// same launch publishes them); otherwise chain-major.
+// ---------------------------------------------------------------------------------------------
+LUCID_HD bool dk_item(int ticket, int C, int T, bool follow, bool split, bool diag_tiles, int& chain, int& i,
+                      int& n_low, int& q0, int& q1) {
+  const int half = split ? (ticket & 1) : 0;
+  if (split) ticket >>= 1;
+  if (ticket < 0 || ticket >= C * T) return false;
+  if (follow) {
+    chain = ticket % C;
+    i = T - 1 - ticket / C;
+  } else {
+    chain = ticket / T;
+    i = ticket % T;
+  }
+  n_low = i + (diag_tiles ? 1 : 0);
+  const int n = T - 1 + (diag_tiles ? 2 : 0);
+  q0 = 0;
+  q1 = n;
+  if (split) {
+    if (half) q0 = n >> 1;
+    else q1 = n >> 1;
+  }
+  return true;
+}
+// column block of tile q
+LUCID_HD int dk_tile_j(int n_low, int q, bool diag_tiles) {
+  if (q < n_low) return q;                       // 0 .. i-1, then i (D1)
+  return diag_tiles ? q - 1 : q + 1;             // i (D2), i+1 .. | i+1 ..
+}
+// The single A buffer: loaded before the item's first tile (dV_i if that tile is a lower one, else V'_i) and
+// again where the tiles change from lower to upper inside the item; the product issuer waits for a load at
+// the same tiles and frees the buffer after the last tile that uses each load.
+LUCID_HD bool dk_first_a_is_dv(int q0, int n_low) { return q0 < n_low; }
+LUCID_HD bool dk_reloads_a_at(int q, int q0, int n_low) { return q == n_low && q0 < n_low; }
+LUCID_HD bool dk_waits_a_at(int q, int q0, int n_low) { return q == q0 || dk_reloads_a_at(q, q0, n_low); }
+LUCID_HD bool dk_frees_a_after(int q, int q0, int q1, int n_low) {
+  return (q == n_low - 1 && q0 < n_low) || q == q1 - 1;
+}
+
 }  // namespace lucid

@@ -157,3 +157,22 @@ def test_work_item_order_keeps_every_chain_in_step_order(tmp_path):
     out = subprocess.run([exe, *cases], capture_output=True, text=True)
     assert out.returncode == 0, out.stdout
     assert out.stdout.strip() == f"ok {len(cases)}"
+
+
+def test_dk_work_items_cover_every_tile_and_balance_the_a_buffer(tmp_path):
+    """The dK kernel's work items (csrc/schedule.h) on the host: whole and split items, both ticket orders,
+    with and without diagonal tiles, T = 1..40: every tile once, the right operand in the A buffer, and as many
+    loads as waits as frees of it (tests/host/dk_items.cpp)."""
+    import shutil
+    import subprocess
+
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no host compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "dk_items")
+    subprocess.run([gxx, "-O1", "-std=c++17", "-I", os.path.join(root, "lucid_kernels_b200", "csrc"), "-o", exe,
+                    os.path.join(root, "tests", "host", "dk_items.cpp")], check=True)
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout
+    assert out.stdout.startswith("ok ")
