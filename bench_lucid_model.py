@@ -12,9 +12,14 @@ uniform-random token ids (synthetic: no dataset or checkpoint is involved).
 Everything around the LUCID solve is plain PyTorch (cuBLAS GEMMs, torch SDPA): plumbing that is identical
 in both variants, so that the difference between the two is the cost of the solve and its call-site glue.
 
-    python bench_lucid_model.py [--seqlens 2048 8192 32768 65536] [--iters 5]
+    python bench_lucid_model.py [--seqlens 2048 8192 32768 65536] [--iters 5] [--vprime-residency]
 
-Prints one JSON line per sequence length: tokens/s of both variants and the LUCID overhead.
+Prints one JSON line per sequence length: tokens/s of both variants and the LUCID overhead.  With
+--vprime-residency it also times, per sequence length, a global layer's attention call straight after the
+solve that produced V' (V' as warm in the L2 cache as the solve leaves it) and after the L2 has been
+overwritten (V' read back from HBM): the difference is what keeping V' resident for, or fusing its
+production with, the attention of the same layer (the step after the solve at the reference's call site,
+bench_lucid_model.py:189-193) could save at most.
 """
 from __future__ import annotations
 
@@ -94,8 +99,10 @@ class Model:
         self.norm = torch.ones(c["hidden"], device=device, dtype=dtype)
 
     @torch.no_grad()
-    def prefill(self, ids, lucid: bool):
-        """Returns the last position's logits.  `lucid`: apply the LUCID solve to K/V of the global layers."""
+    def prefill(self, ids, lucid: bool, tap=None):
+        """Returns the last position's logits.  `lucid`: apply the LUCID solve to K/V of the global layers.
+        `tap`: a list that receives (layer index, k, v, v_prime, k_scale) of every solve, k and v being the
+        BSHD views handed to it."""
         from lucid_kernels_b200.cute import _forward_sub_fwd
 
         c = CFG
@@ -123,6 +130,8 @@ class Model:
                     # to k in a pass of its own
                     ks = D ** -0.25
                     v_prime = _forward_sub_fwd(k.transpose(1, 2), v.transpose(1, 2), k_scale=ks)
+                    if tap is not None:
+                        tap.append((li, k.transpose(1, 2), v.transpose(1, 2), v_prime, ks))
                     v = v_prime.transpose(1, 2)
                     scale = ks / math.sqrt(D)                          # q . (ks k) / sqrt(d)
                 a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True, scale=scale)
@@ -137,10 +146,47 @@ class Model:
         return last @ self.embed.T
 
 
+@torch.no_grad()
+def vprime_residency_probe(N, dev, iters=10):
+    """One global layer's solve followed by its attention call, at the model's head counts: attention timed
+    with V' as the solve left it (warm) and after 256 MiB of other writes went through the L2 (cold)."""
+    from lucid_kernels_b200.cute import _forward_sub_fwd
+
+    c = CFG
+    D, Hq, Hkv = c["head_dim"], c["q_heads"], c["kv_heads"]
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    q = torch.randn(1, Hq, N, D, device=dev, dtype=torch.bfloat16, generator=g)
+    k = torch.randn(1, Hkv, N, D, device=dev, dtype=torch.bfloat16, generator=g)
+    v = torch.randn(1, Hkv, N, D, device=dev, dtype=torch.bfloat16, generator=g)
+    ks = D ** -0.25
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    res = {}
+    for name, evict in (("warm", False), ("cold", True)):
+        tot = 0.0
+        for it in range(iters + 2):
+            vp = _forward_sub_fwd(k.transpose(1, 2), v.transpose(1, 2), k_scale=ks).transpose(1, 2)
+            if evict:
+                flush.fill_(it & 255)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            F.scaled_dot_product_attention(q, k, vp, is_causal=True, enable_gqa=True, scale=ks / math.sqrt(D))
+            b.record()
+            torch.cuda.synchronize()
+            if it >= 2:
+                tot += a.elapsed_time(b)
+        res[name] = tot / iters
+    vp_bytes = N * Hkv * D * 2
+    return dict(seqlen=N, attention_ms_vprime_warm=res["warm"], attention_ms_vprime_cold=res["cold"],
+                saving_ms=res["cold"] - res["warm"], vprime_bytes=vp_bytes,
+                hbm_round_trip_ms_at_6_5_TBps=2 * vp_bytes / 6.5e12 * 1e3)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--seqlens", type=int, nargs="+", default=[2048, 8192, 32768, 65536])
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--vprime-residency", action="store_true")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "needs a CUDA device"
     dev = torch.device("cuda", 0)
@@ -168,6 +214,8 @@ def main():
                               config="Gemma-3-4B-style: 34 layers (5 global + LUCID, 29 sliding window 1024), "
                                      "hidden 2560, 8q/4kv heads, d 128, GeGLU 10240, vocab 262144",
                               softmax=res["softmax"], lucid=res["lucid"], lucid_overhead=over)), flush=True)
+        if args.vprime_residency:
+            print(json.dumps(dict(metric="vprime_residency", **vprime_residency_probe(N, dev))), flush=True)
 
 
 if __name__ == "__main__":

@@ -8,7 +8,10 @@
  *
  * Tensors are (B, N, H, 128) fp16 or bf16 with a contiguous last dimension ("BSHD"); `*_strides`
  * give the element strides of the first three dimensions {batch, sequence, head}.  Base addresses
- * must be 16-byte aligned and the strides multiples of 8 elements.  N must be a multiple of 128.
+ * must be 16-byte aligned and the strides multiples of 8 elements; a dimension of extent 1 may carry any
+ * such stride, a longer one must not have stride 0 (expanded tensors are refused with LUCID_E_BAD_STRIDE:
+ * the reference makes such inputs contiguous first, forward_sub_interface.py:26-27,81).  N must be a
+ * multiple of 128.
  *
  * Return value: 0 on success, a negative LUCID_E_* code for a rejected argument, or a positive
  * cudaError_t from the runtime.  Device-side waits are bounded; a wait that runs out does not hang
@@ -48,6 +51,7 @@ extern "C" {
 #define LUCID_E_TENSOR_MAP (-6)
 #define LUCID_E_NO_DEVICE (-7)
 #define LUCID_E_STATIC_SCRATCH_TOO_SMALL (-8)
+#define LUCID_E_BAD_STRIDE (-9)   /* zero stride in a dimension of extent > 1 (an expanded tensor) */
 
 /* Size of the scratch array that lucid_fwd_sub_static() keeps inside the library (per GPU). */
 #define LUCID_STATIC_SCRATCH_BYTES (9u << 20)
@@ -60,9 +64,14 @@ extern "C" {
  * allocations of forward_sub_interface.py:97-103,217-219,297-300 and the diag_inv tensor of :109-117. */
 size_t lucid_workspace_bytes(int B, int N, int H);
 
+/* The part of that workspace a forward call (or a dV-only backward call) needs: everything except the dK
+ * partial sums.  lucid_fwd_sub accepts a workspace of this size. */
+size_t lucid_fwd_workspace_bytes(int B, int N, int H);
+
 /* V' = L^-1 V.  Replaces _forward_sub_fwd (forward_sub_interface.py:56-165): _compute_diag_inv (:30-53)
- * and the ForwardSubSm90 launch (:153-158).  `window_blocks` <= 0 means full causality, otherwise
- * only the last `window_blocks` blocks are subtracted (forward_sub_interface.py:69-70).
+ * and the ForwardSubSm90 launch (:153-158).  `window_blocks` < 0 means full causality (the reference's
+ * window_size=None); otherwise only the last `window_blocks` blocks are subtracted, 0 meaning none at all,
+ * i.e. only the diagonal-block solve (n_block_count = min(m_block, window_size), forward_sub_fwd.py:518-519).
  * `chain_group` = how many (batch, head) systems the scheduler advances together (0 = choose from the
  * problem size so that their K and V' fit the L2 cache). */
 int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
@@ -83,15 +92,20 @@ int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_s
  * process exits).  The call path performs no cudaMalloc, cudaFree or allocating library call.
  *
  * Limits and rules:
- *  - the problem must fit the array: lucid_workspace_bytes(B, N, H) <= 9 MiB minus alignment, i.e. up to
- *    B*H*N = 32768 rows (for example B=1, H=2, N=16384, or B=2, H=4, N=4096); larger problems are refused
- *    with LUCID_E_STATIC_SCRATCH_TOO_SMALL and nothing is launched;
- *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
- *    first call outside any stream capture;
+ *  - the problem must fit the array: lucid_fwd_workspace_bytes(B, N, H) <= LUCID_STATIC_SCRATCH_BYTES - 1023
+ *    (the array is re-aligned to 1 KiB), about 33 KiB per 128 rows, i.e. up to B*H*N = 36096 rows (for
+ *    example B=1, H=2, N=16384, or B=2, H=4, N=4096); larger problems are refused with
+ *    LUCID_E_STATIC_SCRATCH_TOO_SMALL and nothing is launched;
+ *  - make the FIRST call on each device at start-up, as a warm-up, outside any stream capture: it looks up
+ *    the array's device address (cudaGetSymbolAddress), and with CUDA's lazy module loading that is also
+ *    the moment the driver loads this library's device code and reserves the 9 MiB array on that GPU - the
+ *    one step on this path that takes device memory, and one that can fail on a GPU that is already full.
+ *    Later calls take nothing;
  *  - all calls on a device share the one array, so two calls that can overlap on the GPU (different
  *    streams, or host threads) race with each other: serialise them;
  *  - the array keeps the previous call's contents; the call clears what must start at zero (flags and
- *    control words) itself and always recomputes the diagonal inverses (LUCID_FLAG_REUSE_DIAG is ignored);
+ *    control words) itself and always recomputes the diagonal inverses; LUCID_FLAG_REUSE_DIAG and
+ *    LUCID_FLAG_INSTRUMENT are ignored (the caller has no pointer to read timestamps back through);
  *  - status_out may be NULL (nothing synchronises); if it is not, the call synchronises cuda_stream and
  *    fills it exactly like lucid_read_status().
  * All other arguments are those of lucid_fwd_sub. */
@@ -169,7 +183,21 @@ void lucid_set_fused_backward(int max_chains, int solve_ctas);
  * which publishes every row-block through global memory (forward_sub_fwd.py:536-544). */
 void lucid_set_pair_solve(int max_chains);
 
-/* Per-kernel timing for benchmarks: the NEXT lucid_fwd_sub / lucid_bwd_sub call records these
+/* The same switch with its second limit: pairs are used with at most `max_chains` systems and at most
+ * `max_row_blocks` 128-row blocks over all systems (B*H*N/128; default 768; <= 0 restores the default). */
+void lucid_set_pair_limits(int max_chains, int max_row_blocks);
+
+/* 1 if lucid_fwd_sub with the diagonal solve and full causality would run this problem in that pair mode
+ * under the current limits, else 0 (benchmarks use it to label what they measured). */
+int lucid_query_pair_solve(int B, int N, int H);
+
+/* The id of the capture `cuda_stream` is recording into (cudaStreamGetCaptureInfo), 0 when it is not
+ * capturing.  Host layers that remember what a workspace holds between calls use it to keep work recorded
+ * into a CUDA graph (which runs later, at replay) apart from work that ran at once.  No counterpart in the
+ * reference. */
+unsigned long long lucid_stream_capture_id(void* cuda_stream);
+
+/* Per-kernel timing for benchmarks: the NEXT lucid_fwd_sub / lucid_bwd_sub call made BY THE CALLING THREAD records these
  * cudaEvent_t handles on its stream (before the diagonal-prep kernel, after it, after the solve kernel,
  * after the dK kernel); any of them may be NULL.  The handles are forgotten after that call.  Stands in
  * for the reference's `instrument=True` compile flag (forward_sub_interface.py:62) at kernel granularity. */

@@ -30,7 +30,7 @@ EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_rea
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
            "lucid_profile_next_call", "lucid_set_head_steps", "lucid_set_group_overlap", "lucid_set_dk_split", "lucid_fwd_sub_static",
            "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled",
-           "lucid_set_pair_solve")
+           "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve")
 
 
 class LucidKernelError(RuntimeError):
@@ -57,6 +57,14 @@ def load() -> ctypes.CDLL:
         c = ctypes
         lib.lucid_workspace_bytes.restype = c.c_size_t
         lib.lucid_workspace_bytes.argtypes = [c.c_int, c.c_int, c.c_int]
+        lib.lucid_fwd_workspace_bytes.restype = c.c_size_t
+        lib.lucid_fwd_workspace_bytes.argtypes = [c.c_int, c.c_int, c.c_int]
+        lib.lucid_stream_capture_id.restype = c.c_ulonglong
+        lib.lucid_stream_capture_id.argtypes = [c.c_void_p]
+        lib.lucid_query_pair_solve.restype = c.c_int
+        lib.lucid_query_pair_solve.argtypes = [c.c_int, c.c_int, c.c_int]
+        lib.lucid_set_pair_limits.restype = None
+        lib.lucid_set_pair_limits.argtypes = [c.c_int, c.c_int]
         lib.lucid_workspace_timestamps_offset.restype = c.c_size_t
         lib.lucid_workspace_timestamps_offset.argtypes = [c.c_int, c.c_int, c.c_int]
         lib.lucid_fwd_sub.restype = c.c_int
@@ -98,11 +106,13 @@ def load() -> ctypes.CDLL:
             lib.lucid_set_head_steps(int(os.environ["LUCID_B200_HEAD_STEPS"]))
         lib.lucid_set_pair_solve.restype = None
         lib.lucid_set_pair_solve.argtypes = [c.c_int]
+        # LUCID_B200_PAIR_SOLVE="max_chains[,max_row_blocks]"
         if os.environ.get("LUCID_B200_PAIR_SOLVE"):
-            lib.lucid_set_pair_solve(int(os.environ["LUCID_B200_PAIR_SOLVE"]))
+            parts = [int(x) for x in os.environ["LUCID_B200_PAIR_SOLVE"].split(",")]
+            lib.lucid_set_pair_limits(parts[0], parts[1] if len(parts) > 1 else 0)
         lib.lucid_set_fused_backward.restype = None
         lib.lucid_set_fused_backward.argtypes = [c.c_int, c.c_int]
-        # LUCID_B200_FUSED_BWD="max_chains[,solve_ctas]" overrides the library's default (4, automatic)
+        # LUCID_B200_FUSED_BWD="max_chains[,solve_ctas]" overrides the library's default (2, automatic)
         env = os.environ.get("LUCID_B200_FUSED_BWD")
         if env:
             parts = [int(x) for x in env.split(",")]
@@ -128,47 +138,64 @@ def dtype_code(dt: torch.dtype) -> int:
     raise AssertionError("inputs must be float16 or bfloat16")
 
 
-# One workspace per (device, stream, problem size): the kernels of one call communicate through it, so
-# two calls that may overlap on the GPU must not share one.
-_workspaces: Dict[Tuple[int, int, int, int, int], torch.Tensor] = {}
+# One workspace per (device, stream, capture, problem size): the kernels of one call communicate through it,
+# so two calls that may overlap on the GPU must not share one.  Calls recorded into a CUDA graph get a
+# workspace of their own per capture: they run later, at replay, and must neither disturb nor trust what
+# eager calls (or another graph) leave in theirs.
+class _Workspace:
+    __slots__ = ("buf", "diag")
+
+    def __init__(self, buf: torch.Tensor):
+        self.buf = buf
+        self.diag = None          # what the diagonal-block inverses in `buf` were last prepared for
 
 
-def workspace(device: torch.device, stream_ptr: int, B: int, N: int, H: int) -> torch.Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr, B, N, H)
-    ws = _workspaces.get(key)
-    if ws is None:
-        nbytes = load().lucid_workspace_bytes(B, N, H)
+_workspaces: Dict[Tuple[int, int, int, int, int, int], _Workspace] = {}
+_MAX_WORKSPACES = 64
+
+
+def _entry(device: torch.device, stream_ptr: int, B: int, N: int, H: int) -> _Workspace:
+    lib = load()
+    cap = int(lib.lucid_stream_capture_id(stream_ptr))
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr, cap, B, N, H)
+    ent = _workspaces.get(key)
+    if ent is None:
+        nbytes = lib.lucid_workspace_bytes(B, N, H)
         # torch's caching allocator hands out 512-byte aligned blocks; over-allocate to reach 1 KiB
         raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
         off = (-raw.data_ptr()) % 1024
-        ws = raw[off:off + nbytes]
-        if len(_workspaces) > 64:
-            _workspaces.clear()
-        _workspaces[key] = ws
-    return ws
+        ent = _Workspace(raw[off:off + nbytes])
+        if len(_workspaces) >= _MAX_WORKSPACES:
+            # drop the oldest entry only (dict order = insertion order), with what it remembered
+            _workspaces.pop(next(iter(_workspaces)))
+        _workspaces[key] = ent
+    return ent
 
 
-# What each workspace last prepared its diagonal-block inverses for.  They depend on k only, so a
-# backward call that follows the forward call on the same k can skip recomputing them.  "Same k" means
-# the same live tensor object with an unchanged version counter: the address alone is not enough,
-# because the caching allocator hands a freed block to the next tensor of that size.
-_diag_keys: Dict[int, tuple] = {}
+def workspace(device: torch.device, stream_ptr: int, B: int, N: int, H: int) -> torch.Tensor:
+    return _entry(device, stream_ptr, B, N, H).buf
 
 
+# The inverses depend on k only, so a backward call that follows the forward call on the same k can skip
+# recomputing them - when the caller asks for that (``reuse_diag=True``; the autograd wrapper does, because
+# autograd itself refuses to run a backward whose saved k was modified).  "Same k" means the same live
+# tensor object with an unchanged version counter: the address alone is not enough, because the caching
+# allocator hands a freed block to the next tensor of that size.  The note lives with the workspace it
+# describes, so it goes when the workspace goes.
 def _diag_key(k: torch.Tensor) -> tuple:
     return (k.data_ptr(), k._version, tuple(k.shape), tuple(k.stride()), k.dtype)
 
 
-def diag_is_cached(ws: torch.Tensor, k: torch.Tensor, k_scale: float = 1.0) -> bool:
-    entry = _diag_keys.get(ws.data_ptr())
+def diag_is_cached(device: torch.device, stream_ptr: int, k: torch.Tensor, k_scale: float = 1.0) -> bool:
+    B, N, H, _ = k.shape
+    entry = _entry(device, stream_ptr, B, N, H).diag
     return entry is not None and entry[0]() is k and entry[1] == (_diag_key(k), float(k_scale))
 
 
-def diag_remember(ws: torch.Tensor, k: torch.Tensor, valid: bool, k_scale: float = 1.0) -> None:
-    if valid:
-        _diag_keys[ws.data_ptr()] = (weakref.ref(k), (_diag_key(k), float(k_scale)))
-    else:
-        _diag_keys.pop(ws.data_ptr(), None)
+def diag_remember(device: torch.device, stream_ptr: int, k: torch.Tensor, valid: bool, k_scale: float = 1.0) -> None:
+    B, N, H, _ = k.shape
+    ent = _entry(device, stream_ptr, B, N, H)
+    ent.diag = (weakref.ref(k), (_diag_key(k), float(k_scale))) if valid else None
 
 
 def check_rc(rc: int, what: str) -> None:

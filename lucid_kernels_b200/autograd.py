@@ -2,7 +2,9 @@
 
 Mirrors ``LUCIDForwardSub`` of the reference's benchmark scripts (bench_lucid_model.py:34-51,
 bench_lucid_e2e.py:34-49): forward saves ``(k, v_prime)``, backward returns ``(dk, dv)`` in the order of
-the inputs ``(k, v)``.
+the inputs ``(k, v)``.  The backward reuses the diagonal-block inverses the forward left in the workspace
+when they are still there: autograd refuses to run a backward whose saved ``k`` was modified in place, so
+between the two calls of one node ``k`` is known to be unchanged.
 """
 from __future__ import annotations
 
@@ -26,7 +28,7 @@ class LUCIDForwardSub(torch.autograd.Function):
     def backward(ctx, dv_prime):
         k, v_prime = ctx.saved_tensors
         dv, dk = _forward_sub_bwd(k, v_prime, dv_prime, block_size=ctx.block_size, use_diag_solve=True,
-                                  use_combined_kernel=True, k_scale=ctx.k_scale)
+                                  use_combined_kernel=True, k_scale=ctx.k_scale, reuse_diag=True)
         return dk, dv, None, None
 
 

@@ -9,12 +9,14 @@
 namespace lucid {
 
 static unsigned long long g_wait_ns = 2000000000ull;
-// optional per-kernel timing: events recorded around the kernels of the NEXT call, then forgotten
-static cudaEvent_t g_events[4] = {nullptr, nullptr, nullptr, nullptr};
+// optional per-kernel timing: events recorded around the kernels of the NEXT call made by the same host
+// thread, then forgotten (thread-local, so one thread's request is never consumed by another thread's call)
+static thread_local cudaEvent_t g_events[4] = {nullptr, nullptr, nullptr, nullptr};
 static long long* g_trace = nullptr;
 static int g_fuse_max_chains = 2;   // combined backward: fuse solve and dK into one launch up to this many chains
 static int g_fuse_solve_ctas = 0;   // 0 = automatic share
 static int g_pair_max_chains = 8;   // solve pairs of row-blocks with clusters of two CTAs up to this many chains
+static int g_pair_max_blocks = 768; // ... and up to this many row-blocks in all (chains * T)
 static int g_head = -1;   // scheduler knob; < 0 = default
 static int g_overlap = -1;   // scheduler knob; < 0 = default
 static int g_dk_split = 1;   // one-launch backward: dK row-blocks as two work items
@@ -23,7 +25,8 @@ static inline void record_event(int i, cudaStream_t stream) {
 }
 
 // ---- workspace layout ----------------------------------------------------------------------
-//   [0, 256)            three Control blocks: 0 = diag prep, 1 = solve, 2 = dK
+//   [0, 256)            three Control blocks: 0 = diag prep, 1 = solve, 2 = dK; word 24 = arrival counter of the
+//                       one-launch backward (which CTAs take the solve role)
 //   [256, 256 + 4*C*T)  flags
 //   X                   C*T tiles of 32 KiB (1 KiB aligned)
 //   lam_inv             C*T*128 fp32
@@ -62,11 +65,17 @@ static int sm_count() {
   return cached[dev];
 }
 
-static int check_tensor(const void* p, const int64_t st[3]) {
+// st = element strides {batch, sequence, head}; ext = the extents of those dimensions.  A zero stride in a
+// dimension of extent > 1 is an expanded (broadcast) tensor: the tensor maps cannot express it, and writing
+// through one would alias.
+static int check_tensor(const void* p, const int64_t st[3], int B, int N, int H) {
   if (!p || !st) return LUCID_E_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(p) % 16) return LUCID_E_BAD_ALIGNMENT;
-  for (int i = 0; i < 3; ++i)
+  const int ext[3] = {B, N, H};
+  for (int i = 0; i < 3; ++i) {
     if (st[i] % 8 || st[i] < 0) return LUCID_E_BAD_ALIGNMENT;
+    if (st[i] == 0 && ext[i] > 1) return LUCID_E_BAD_STRIDE;
+  }
   return 0;
 }
 
@@ -81,11 +90,12 @@ static int check_shape(int B, int N, int H, int D, int dtype) {
 static int bshd_map(CUtensorMap* m, bool bf16, const void* p, const int64_t st[3], int B, int N, int H,
                     uint32_t box_rows) {
   uint64_t dims[4] = {(uint64_t)kBlock, (uint64_t)N, (uint64_t)H, (uint64_t)B};
-  // size-1 dimensions may carry any stride; give them a harmless valid one
+  // size-1 dimensions may carry any stride; give them a harmless valid one.  (Zero strides of longer
+  // dimensions never get here: check_tensor refuses them.)
   uint64_t sn = (uint64_t)st[1] * 2, sh = (uint64_t)st[2] * 2, sb = (uint64_t)st[0] * 2;
-  if (H == 1 || sh == 0) sh = 256;
-  if (B == 1 || sb == 0) sb = 256;
-  if (sn == 0) sn = 256;
+  if (H == 1) sh = 256;
+  if (B == 1) sb = 256;
+  if (sn == 0 || sh == 0 || sb == 0) return LUCID_E_BAD_STRIDE;
   uint64_t strides[3] = {sn, sh, sb};
   return make_tmap_16bit(m, bf16, p, 4, dims, strides, box_rows) ? LUCID_E_TENSOR_MAP : 0;
 }
@@ -135,6 +145,12 @@ static Problem make_problem(int B, int N, int H, int flags, int window, int grou
   p.reuse_diag = (flags & LUCID_FLAG_REUSE_DIAG) ? 1 : 0;
   p.wait_ns = g_wait_ns;
   return p;
+}
+
+// Whether a stand-alone solve of this problem runs as clusters of two CTAs over pairs of row-blocks.
+static bool pair_eligible(const Problem& p) {
+  return p.C <= g_pair_max_chains && p.C * p.T <= g_pair_max_blocks && p.use_diag && p.window < 0 && !p.no_sync &&
+         (p.T % 2) == 0 && p.head == 0 && p.overlap == 0;
 }
 
 // What the combined backward hands to run_solve when the dK program is to run in the solve's launch.
@@ -191,7 +207,7 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
     fused->args.follow_flags = sa.flags;
     fused->args.follow_ctl = sa.ctl;
     e = launch_bwd_fused(bf16, tm_k, tm_in, tm_out, tm_x, tm_st, fused->tm_vp, fused->tm_dv, sa, fused->args,
-                         fused->n_solve, sms, stream);
+                         fused->n_solve, reinterpret_cast<int*>(ws) + 24, sms, stream);
   } else {
     // Few chains: the hand-over latency between consecutive row-blocks limits the solve; pairs of row-blocks
     // are then solved by clusters of two CTAs, the first handing its result to the second through shared memory.
@@ -199,8 +215,7 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
     // on B200 (forward, ms, pairs against single row-blocks: 8 chains of N=8192 0.255 / 0.270, 1 and 2 chains of
     // N=32768 0.82 / 0.93 and 0.95 / 1.00, but 4 chains of N=65536 5.5 / 4.9 - the pairs are taken in a fixed
     // rotation, which balances the tile work less well than the ticket counter).
-    const bool pair = p.C <= g_pair_max_chains && p.C * p.T <= 768 && p.use_diag && p.window <= 0 && !p.no_sync &&
-                      (p.T % 2) == 0 && p.head == 0;
+    const bool pair = pair_eligible(p);
     int pgrid = grid;
     if (pair) {
       const int items = CT / 2;
@@ -229,6 +244,21 @@ size_t lucid_workspace_bytes(int B, int N, int H) {
   return make_layout(B, N, H).total;
 }
 
+size_t lucid_fwd_workspace_bytes(int B, int N, int H) {
+  if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
+  return make_layout(B, N, H).need;
+}
+
+unsigned long long lucid_stream_capture_id(void* cuda_stream) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  unsigned long long id = 0;
+  if (cudaStreamGetCaptureInfo(static_cast<cudaStream_t>(cuda_stream), &st, &id) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return st == cudaStreamCaptureStatusActive ? id : 0;
+}
+
 size_t lucid_workspace_timestamps_offset(int B, int N, int H) {
   if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
   return make_layout(B, N, H).ts;
@@ -242,7 +272,17 @@ void lucid_set_group_overlap(int steps) { g_overlap = steps; }
 
 void lucid_set_dk_split(int on) { g_dk_split = on; }
 
+int lucid_query_pair_solve(int B, int N, int H) {
+  if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
+  return pair_eligible(make_problem(B, N, H, LUCID_FLAG_DIAG_SOLVE, -1, 0, 1.0f)) ? 1 : 0;
+}
+
 void lucid_set_pair_solve(int max_chains) { g_pair_max_chains = max_chains; }
+
+void lucid_set_pair_limits(int max_chains, int max_row_blocks) {
+  g_pair_max_chains = max_chains;
+  g_pair_max_blocks = max_row_blocks > 0 ? max_row_blocks : 768;
+}
 
 void lucid_set_fused_backward(int max_chains, int solve_ctas) {
   g_fuse_max_chains = max_chains;
@@ -275,8 +315,8 @@ int lucid_fwd_sub_scaled(const void* k, const void* v, void* v_prime, const int6
   int rc;
   if (!(k_scale > 0.0f) || !(k_scale < 1e18f)) return LUCID_E_BAD_SHAPE;
   if ((rc = check_shape(B, N, H, D, dtype))) return rc;
-  if ((rc = check_tensor(k, k_strides)) || (rc = check_tensor(v, v_strides)) ||
-      (rc = check_tensor(v_prime, vp_strides)))
+  if ((rc = check_tensor(k, k_strides, B, N, H)) || (rc = check_tensor(v, v_strides, B, N, H)) ||
+      (rc = check_tensor(v_prime, vp_strides, B, N, H)))
     return rc;
   if (!workspace) return LUCID_E_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) % 1024) return LUCID_E_BAD_ALIGNMENT;
@@ -323,8 +363,9 @@ int lucid_fwd_sub_static(const void* k, const void* v, void* v_prime, const int6
   const size_t usable = LUCID_STATIC_SCRATCH_BYTES - (aligned - base);
   const size_t need = make_layout(B, N, H).need;
   if (need > usable) return LUCID_E_STATIC_SCRATCH_TOO_SMALL;
-  // the array still holds whatever the previous call left: never trust a cached inverse in it
-  flags &= ~LUCID_FLAG_REUSE_DIAG;
+  // the array still holds whatever the previous call left: never trust a cached inverse in it; and the caller
+  // has no pointer through which it could read instrumentation back
+  flags &= ~(LUCID_FLAG_REUSE_DIAG | LUCID_FLAG_INSTRUMENT);
   rc = lucid_fwd_sub(k, v, v_prime, k_strides, v_strides, vp_strides, B, N, H, D, dtype, flags, window_blocks,
                      chain_group, reinterpret_cast<void*>(aligned), usable, cuda_stream);
   if (rc) return rc;
@@ -350,11 +391,11 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
   if (!(k_scale > 0.0f) || !(k_scale < 1e18f)) return LUCID_E_BAD_SHAPE;
   if ((rc = check_shape(B, N, H, D, dtype))) return rc;
   if (mode != LUCID_BWD_DV_ONLY && mode != LUCID_BWD_COMBINED) return LUCID_E_BAD_SHAPE;
-  if ((rc = check_tensor(k, k_strides)) || (rc = check_tensor(dv_prime, dvp_strides)) ||
-      (rc = check_tensor(dv, dv_strides)))
+  if ((rc = check_tensor(k, k_strides, B, N, H)) || (rc = check_tensor(dv_prime, dvp_strides, B, N, H)) ||
+      (rc = check_tensor(dv, dv_strides, B, N, H)))
     return rc;
   if (mode == LUCID_BWD_COMBINED) {
-    if ((rc = check_tensor(v_prime, vp_strides)) || (rc = check_tensor(dk, dk_strides))) return rc;
+    if ((rc = check_tensor(v_prime, vp_strides, B, N, H)) || (rc = check_tensor(dk, dk_strides, B, N, H))) return rc;
   }
   if (!workspace) return LUCID_E_NULL_POINTER;
   if (reinterpret_cast<uintptr_t>(workspace) % 1024) return LUCID_E_BAD_ALIGNMENT;
@@ -365,7 +406,7 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
   cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);
   if (e != cudaSuccess) return (int)e;
   const bool bf16 = dtype == LUCID_DTYPE_BF16;
-  const Problem p = make_problem(B, N, H, flags, 0, chain_group, k_scale);
+  const Problem p = make_problem(B, N, H, flags, -1, chain_group, k_scale);
   const int sms = sm_count();
   if (sms <= 0) return LUCID_E_NO_DEVICE;
   const int CT = p.C * p.T;
@@ -453,8 +494,11 @@ const char* lucid_status_string(int code) {
     case LUCID_E_NULL_POINTER: return "null pointer";
     case LUCID_E_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected a tensor";
     case LUCID_E_NO_DEVICE: return "no CUDA device";
+    case LUCID_E_BAD_STRIDE:
+      return "zero stride in a dimension of extent > 1 (expanded tensor): make the tensor contiguous first";
     case LUCID_E_STATIC_SCRATCH_TOO_SMALL:
-      return "problem too large for the library-owned scratch of lucid_fwd_sub_static (9 MiB: B*H*N <= 32768 rows)";
+      return "problem too large for the library-owned scratch of lucid_fwd_sub_static "
+             "(lucid_workspace_bytes(B, N, H) must not exceed LUCID_STATIC_SCRATCH_BYTES - 1023)";
     default: return code > 0 ? "CUDA runtime error" : "unknown";
   }
 }

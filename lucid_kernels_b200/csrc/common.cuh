@@ -39,7 +39,7 @@ struct Problem {
   int head;          // leading steps that are scheduled for all chains together before the groups start
   int overlap;       // steps of a group's start that are dealt out alternately with the previous group's end
   int use_diag;      // apply the diagonal-block solve
-  int window;        // forward only: number of previous blocks used (<= 0: all)
+  int window;        // forward only: number of previous blocks used (< 0: all, 0: none)
   int no_sync;       // skip flag waits (profiling only; results are then meaningless)
   int instrument;    // write per-row-block timestamps
   int reuse_diag;    // the workspace already holds X and lam_inv for this K (host decides)

@@ -140,6 +140,12 @@ __global__ void __launch_bounds__(128) diag_prep_kernel(const __grid_constant__ 
     }
   }
   __syncthreads();
+  if (s.abort_flag) {
+    // a wait ran out: give the tile load that may still be in flight time to land before this CTA's shared
+    // memory is handed to another CTA
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 100000ull) __nanosleep(1000);
+  }
   if (ok) {
     const uint4* src = reinterpret_cast<const uint4*>(s.k);
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(args.x) + (long long)blk * kTileBytes);

@@ -46,11 +46,11 @@ cudaError_t launch_diag_prep(bool bf16, const CUtensorMap& tm_k, const PrepArgs&
                              cudaStream_t stream);
 cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,
                       const DkArgs& args, int grid, cudaStream_t stream);
-// Reverse solve (CTAs 0 .. n_solve-1) and dK (the remaining CTAs) in one launch; dargs.follow_flags must
-// point at the solve's flags.  grid must not exceed the number of SMs: the dK CTAs wait for the solve CTAs.
+// Reverse solve (the first n_solve CTAs to start, counted in *arrivals, which must be zero at launch) and dK
+// (the remaining CTAs) in one launch; dargs.follow_flags must point at the solve's flags.
 cudaError_t launch_bwd_fused(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_in, const CUtensorMap& tm_out,
                              const CUtensorMap& tm_x, const CUtensorMap& tm_st, const CUtensorMap& tm_vp,
                              const CUtensorMap& tm_dv, const SolveArgs& sargs, const DkArgs& dargs, int n_solve,
-                             int grid, cudaStream_t stream);
+                             int* arrivals, int grid, cudaStream_t stream);
 
 }  // namespace lucid

@@ -23,8 +23,9 @@
 //
 // Pair mode (few chains, where the hand-over latency between consecutive row-blocks is what limits a
 // chain): the grid is launched as clusters of two CTAs, work items are pairs of consecutive row-blocks of
-// a chain taken in a fixed rotation by the clusters, CTA 0 of a cluster solves the first row-block and
-// CTA 1 the second.  CTA 0 hands its result to CTA 1 directly: CTA 1 claims the two ring stages of its
+// a chain.  CTA 0 of a cluster draws the pair's ticket from the global counter and passes it to CTA 1
+// through a small mailbox in CTA 1's shared memory, so pairs are claimed in dependency order by clusters
+// that are running, exactly like single row-blocks; CTA 0 solves the first row-block and CTA 1 the second.  CTA 0 hands its result to CTA 1 directly: CTA 1 claims the two ring stages of its
 // last tile, arms their barriers with the byte count and bumps a counter in CTA 0's shared memory; CTA 0
 // stages the tile as always and one thread copies it into those stages with four bulk shared-to-shared
 // copies (each with one destination), whose arrival completes CTA 1's stage barriers like a TMA load.  That replaces
@@ -66,12 +67,14 @@ struct SolveSmem {
   uint32_t tmem_base;
   int abort_flag;
   int peer_items;        // pair mode, CTA 0: items for whose handed-over tile CTA 1 has claimed its ring stages
+  int mail[4];           // pair mode, CTA 1: tickets drawn by CTA 0 (item `it` in slot it & 3; -1 = nothing yet)
 };
 
 enum SolveBar : int {
   BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
   BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
-  BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL, BAR_PQ_FULL, BAR_Q_FULL, BAR_PEER_READY
+  BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL, BAR_PQ_FULL, BAR_Q_FULL, BAR_PEER_READY,
+  BAR_PEER_TICKET
 };
 
 // Block size: four service warps plus kG exp groups of four warps (128 threads, one per row).
@@ -145,6 +148,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     mbar_init(&s.q_full, 1);
     s.abort_flag = 0;
     s.peer_items = 0;
+    for (int i = 0; i < 4; ++i) s.mail[i] = -1;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -185,7 +189,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
       jfirst = T - 1;
     } else {
       i = step;
-      n = (P.window > 0) ? min(step, P.window) : step;
+      n = (P.window >= 0) ? min(step, P.window) : step;
       jfirst = i - n;     // visited upward to i-1
     }
     return true;
@@ -207,12 +211,40 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
       bool alive = true;
       int trc = 0;
       (void)trc;
+      int last_ticket = -1;      // pair mode, CTA 1: the newest ticket taken from the mailbox
+      (void)last_ticket;
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_empty[slot], ((it >> 1) & 1) ^ 1, cta_abort, ctl, limit, -1, -1, BAR_TK_EMPTY)) break;
-        // pair mode: both CTAs of a cluster must work on the same pair, so the clusters take the pairs in a
-        // fixed rotation (dependency order is preserved: a cluster's items have increasing tickets)
-        const int ticket = kPair ? (int)(blockIdx.x >> 1) + it * (int)(gridDim.x >> 1) : atomicAdd(&ctl->ticket, 1);
+        // Pair mode: both CTAs of a cluster work on the same pair.  CTA 0 draws the ticket and posts it in
+        // CTA 1's mailbox; CTA 1 takes it from there.  Tickets of a cluster increase, so a slot holds news
+        // once its value exceeds the last ticket seen.  Four slots suffice: CTA 0 draws the ticket of item m
+        // only after all its roles have started item m - 2, i.e. after it handed over the tile of item
+        // m - 3, for which CTA 1 had to have taken ticket m - 3 - so at most three tickets are in flight.
+        int ticket;
+        if (!kPair || crank == 0) {
+          ticket = atomicAdd(&ctl->ticket, 1);
+          if (kPair) st_release_cluster(mapa_u32(smem_u32(&s.mail[it & 3]), 1), ticket);
+        } else {
+          const int* slot_word = &s.mail[it & 3];
+          ticket = ld_acquire_cluster_local(slot_word);
+          if (ticket <= last_ticket) {
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while ((ticket = ld_acquire_cluster_local(slot_word)) <= last_ticket) {
+              if ((++spins & 63u) == 0) {
+                if (*cta_abort) break;
+                if (globaltimer_ns() - t0 > limit) {
+                  *cta_abort = 1;
+                  report_error(ctl, kErrBarrierTimeout, -1, -1, it, BAR_PEER_TICKET);
+                  break;
+                }
+              }
+            }
+            if (ticket <= last_ticket) break;
+          }
+          last_ticket = ticket;
+        }
         s.tk_slot[slot] = ticket;
         mbar_arrive(&s.tk_full[slot]);
         int chain, i, n, jfirst;
@@ -800,6 +832,10 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
   }
 
   // teardown: everybody meets here, also after an abort
+  if (kPair && s.abort_flag && crank == 0 && tid == 0) {
+    // the peer's producer must not wait for tickets that will never be drawn: post one beyond the last item
+    for (int i = 0; i < 4; ++i) st_release_cluster(mapa_u32(smem_u32(&s.mail[i]), 1), 0x7fffffff);
+  }
   if (s.abort_flag) {
     // give copies and MMAs still in flight time to land before shared memory and TMEM are released
     const uint64_t t0 = globaltimer_ns();
@@ -854,7 +890,8 @@ static cudaError_t launch_solve_t(const CUtensorMap& tm_k, const CUtensorMap& tm
     kern<<<grid, solve_threads(kSolveGroups), solve_smem_bytes(), stream>>>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
     return cudaGetLastError();
   }
-  // clusters of two CTAs; every cluster of the grid must be resident (the CTAs wait for one another)
+  // clusters of two CTAs (the two CTAs of a cluster wait for one another; clusters take pairs by ticket, so no
+  // cluster waits for one that is not running); more clusters than fit the device at once would only idle
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(solve_threads(kSolveGroups));

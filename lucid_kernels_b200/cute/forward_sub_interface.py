@@ -14,9 +14,13 @@ is a drop-in for ``from lucid_kernels.cute import ...``.  Differences, all behin
 * ``_forward_sub_bwd_combined`` returns the FULL dK (off-diagonal and diagonal terms);
 * ``use_combined_kernel=False`` still returns the full dK: the dense host formula the reference uses
   there (``_backward_dk_reference``, O(T^2) fp32 temporaries) is an oracle, not a product path;
-* a call whose k is the tensor of the previous call on the same stream (same storage, unchanged
-  version counter), such as the backward after the forward, reuses the diagonal-block inverses
-  still in the workspace (``LUCID_B200_REUSE_DIAG=0`` turns this off);
+* every call recomputes the diagonal-block inverses, as the reference does (:116, :230, :311), unless the
+  caller passes ``reuse_diag=True``: then a call whose k is the very tensor of the previous call on the
+  same stream (same object, unchanged version counter), such as the backward after the forward, reuses
+  the inverses still in the workspace.  The autograd wrapper asks for it; ``LUCID_B200_REUSE_DIAG=1``
+  makes it the default for bare calls too (only safe when nothing writes k behind torch's back);
+* ``window_size=None`` is full causality, ``window_size=0`` subtracts no earlier block at all, as in the
+  reference (``min(m_block, window_size)``, forward_sub_fwd.py:518-519);
 * inter-block waits are bounded: with ``check=True`` (or ``LUCID_B200_CHECK=1``) the call
   synchronises and raises if a wait ran out instead of hanging.
 
@@ -36,10 +40,9 @@ __all__ = ["_forward_sub_fwd", "_forward_sub_bwd", "_forward_sub_bwd_dv", "_forw
 
 _CHECK_DEFAULT = os.environ.get("LUCID_B200_CHECK", "0") not in ("0", "", "false")
 _GROUP_DEFAULT = int(os.environ.get("LUCID_B200_CHAIN_GROUP", "0"))
-# Reuse the diagonal-block inverses left in the workspace by the previous call when k is unchanged (same
-# storage and version counter), e.g. the backward call that follows a forward call.  LUCID_B200_REUSE_DIAG=0
-# recomputes them in every call, as the reference does.
-_REUSE_DIAG = os.environ.get("LUCID_B200_REUSE_DIAG", "1") not in ("0", "", "false")
+# Default of ``reuse_diag`` for bare calls: off, i.e. every call recomputes the diagonal-block inverses as the
+# reference does.  (The version counter torch keeps cannot see writes made through raw pointers.)
+_REUSE_DIAG = os.environ.get("LUCID_B200_REUSE_DIAG", "0") not in ("0", "", "false")
 
 
 def maybe_contiguous(x):
@@ -47,8 +50,10 @@ def maybe_contiguous(x):
 
 
 def _aligned(t: torch.Tensor) -> torch.Tensor:
-    """TMA needs a 16-byte aligned base and strides that are multiples of 16 bytes."""
-    if t.data_ptr() % 16 or any(s % 8 for s in t.stride()[:3]):
+    """TMA needs a 16-byte aligned base and strides that are multiples of 16 bytes; a tensor expanded
+    along a dimension (stride 0, extent > 1) has no tensor map and is materialised."""
+    if t.data_ptr() % 16 or any(s % 8 for s in t.stride()[:3]) or \
+            any(s == 0 and n > 1 for s, n in zip(t.stride()[:3], t.shape[:3])):
         return t.contiguous()
     return t
 
@@ -84,9 +89,10 @@ def _forward_sub_fwd(
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
     k_scale: float = 1.0,
+    reuse_diag: Optional[bool] = None,
 ) -> torch.Tensor:
     """V'_i = inv(tril(exp(K_i K_i^T))) (V_i - sum_{j<i} exp(K_i K_j^T) V'_j)   (diagonal factor only
-    with ``use_diag_solve``; with ``window_size=W`` only the last W blocks are subtracted).
+    with ``use_diag_solve``; with ``window_size=W`` only the last W blocks are subtracted, none for W = 0).
 
     ``k_scale`` (extension): the operator acts on ``k_scale * k`` without the caller having to form that
     tensor (the reference's call site scales by ``d ** -0.25``, bench_lucid_model.py:164-170); the factor is
@@ -107,17 +113,20 @@ def _forward_sub_fwd(
         ws = _cabi.workspace(k.device, stream, B, N, H)
         flags = ((_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_NO_SYNC if no_sync else 0) |
                  (_cabi.FLAG_INSTRUMENT if instrument else 0))
-        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in, k_scale):
+        if window_size is not None:
+            assert int(window_size) >= 0, "window_size must be None or a non-negative number of blocks"
+        if use_diag_solve and (_REUSE_DIAG if reuse_diag is None else reuse_diag) and \
+                _cabi.diag_is_cached(k.device, stream, k_in, k_scale):
             flags |= _cabi.FLAG_REUSE_DIAG
         rc = lib.lucid_fwd_sub_scaled(k.data_ptr(), v.data_ptr(), v_prime.data_ptr(), _cabi.strides3(k),
                                       _cabi.strides3(v), _cabi.strides3(v_prime), B, N, H, D,
                                       _cabi.dtype_code(k.dtype), flags,
-                                      0 if window_size is None else int(window_size),
+                                      -1 if window_size is None else int(window_size),
                                       _GROUP_DEFAULT if chain_group is None else int(chain_group),
                                       float(k_scale), ws.data_ptr(), ws.numel(), stream)
         _cabi.check_rc(rc, "lucid_fwd_sub")
         # the inverses now in the workspace belong to k_in, provided the kernels read k_in's own storage
-        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr(), k_scale)
+        _cabi.diag_remember(k.device, stream, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr(), k_scale)
         if _CHECK_DEFAULT if check is None else check:
             _cabi.raise_on_device_error(ws, stream, "_forward_sub_fwd")
     if instrument:
@@ -126,7 +135,7 @@ def _forward_sub_fwd(
 
 
 def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, chain_group, what, k_in=None,
-              k_scale=1.0):
+              k_scale=1.0, reuse_diag=None):
     B, N, H, D = k.shape
     k_in = k if k_in is None else k_in
     lib = _cabi.load()
@@ -136,7 +145,8 @@ def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, cha
     with torch.cuda.device(k.device):
         ws = _cabi.workspace(k.device, stream, B, N, H)
         flags = (_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_INSTRUMENT if instrument else 0)
-        if use_diag_solve and _REUSE_DIAG and _cabi.diag_is_cached(ws, k_in, k_scale):
+        if use_diag_solve and (_REUSE_DIAG if reuse_diag is None else reuse_diag) and \
+                _cabi.diag_is_cached(k.device, stream, k_in, k_scale):
             flags |= _cabi.FLAG_REUSE_DIAG
         vp_ptr = v_prime.data_ptr() if v_prime is not None else None
         vp_str = _cabi.strides3(v_prime) if v_prime is not None else _cabi.strides3(k)
@@ -148,7 +158,7 @@ def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, cha
                                       _GROUP_DEFAULT if chain_group is None else int(chain_group),
                                       float(k_scale), ws.data_ptr(), ws.numel(), stream)
         _cabi.check_rc(rc, what)
-        _cabi.diag_remember(ws, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr(), k_scale)
+        _cabi.diag_remember(k.device, stream, k_in, use_diag_solve and k.data_ptr() == k_in.data_ptr(), k_scale)
         if _CHECK_DEFAULT if check is None else check:
             _cabi.raise_on_device_error(ws, stream, what)
     ts = _timestamps_view(ws, B, N, H).clone() if instrument else None
@@ -165,6 +175,7 @@ def _forward_sub_bwd_dv(
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
     k_scale: float = 1.0,
+    reuse_diag: Optional[bool] = None,
 ) -> torch.Tensor:
     """dV_i = inv(tril(exp(K_i K_i^T)))^T (dV'_i - sum_{j>i} exp(K_i K_j^T) dV_j), solved from the last
     block to the first."""
@@ -173,7 +184,7 @@ def _forward_sub_bwd_dv(
     k_in = k
     k, dv_prime = _aligned(k.detach()), _aligned(dv_prime.detach())
     dv, _, ts = _bwd_call(k, None, dv_prime, _cabi.BWD_DV_ONLY, use_diag_solve, instrument, check, chain_group,
-                          "_forward_sub_bwd_dv", k_in=k_in, k_scale=k_scale)
+                          "_forward_sub_bwd_dv", k_in=k_in, k_scale=k_scale, reuse_diag=reuse_diag)
     if instrument:
         return dv, ts
     return dv
@@ -190,6 +201,7 @@ def _forward_sub_bwd_combined(
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
     k_scale: float = 1.0,
+    reuse_diag: Optional[bool] = None,
 ) -> tuple:
     """(dv, dk).  Unlike the reference, ``dk`` already contains the diagonal-block term.  With ``k_scale``
     the operator acts on ``k_scale * k`` and ``dk`` is the gradient with respect to ``k`` itself."""
@@ -198,7 +210,7 @@ def _forward_sub_bwd_combined(
     k_in = k
     k, v_prime, dv_prime = [_aligned(t.detach()) for t in (k, v_prime, dv_prime)]
     dv, dk, ts = _bwd_call(k, v_prime, dv_prime, _cabi.BWD_COMBINED, use_diag_solve, instrument, check,
-                           chain_group, "_forward_sub_bwd_combined", k_in=k_in, k_scale=k_scale)
+                           chain_group, "_forward_sub_bwd_combined", k_in=k_in, k_scale=k_scale, reuse_diag=reuse_diag)
     if instrument:
         return dv, dk, ts
     return dv, dk
@@ -215,10 +227,11 @@ def _forward_sub_bwd(
     check: Optional[bool] = None,
     chain_group: Optional[int] = None,
     k_scale: float = 1.0,
+    reuse_diag: Optional[bool] = None,
 ) -> tuple:
     """Full backward pass: returns ``(dv, dk)``, gradients w.r.t. V and K.  Both settings of
     ``use_combined_kernel`` run the same device kernels here."""
     del use_combined_kernel
     return _forward_sub_bwd_combined(k, v_prime, dv_prime, block_size=block_size,
                                      use_diag_solve=use_diag_solve, check=check, chain_group=chain_group,
-                                     k_scale=k_scale)
+                                     k_scale=k_scale, reuse_diag=reuse_diag)

@@ -149,7 +149,10 @@ def test_work_item_order_keeps_every_chain_in_step_order(tmp_path):
     subprocess.run([gxx, "-O1", "-std=c++17", "-I", os.path.join(root, "lucid_kernels_b200", "csrc"), "-o", exe,
                     os.path.join(root, "tests", "host", "ticket_order.cpp")], check=True)
     cases = ["16,256,4,0,0", "16,256,4,0,96", "16,256,4,32,96", "16,256,4,200,28", "16,256,4,200,29",
-             "8,1024,1,0,512", "8,64,2,5,32", "6,10,2,3,3", "5,10,2,2,3", "6,10,3,10,3", "1,7,1,0,3", "3,1,2,0,1"]
+             "8,1024,1,0,512", "8,64,2,5,32", "6,10,2,3,3", "5,10,2,2,3", "6,10,3,10,3", "1,7,1,0,3", "3,1,2,0,1",
+             # pairs of row-blocks solved by clusters of two CTAs: tickets name (chain, pair) with T/2 pairs per
+             # chain, no head and no overlap
+             "8,32,8,0,0", "1,128,1,0,0", "2,128,2,0,0", "16,128,4,0,0", "3,1,3,0,0"]
     rng = random.Random(0)
     for _ in range(200):
         C, T = rng.randint(1, 12), rng.randint(1, 40)

@@ -31,6 +31,16 @@ def test_reduced_model_runs_both_variants(monkeypatch):
     model = m.Model(dev)
     ids = torch.randint(0, 4096, (1, 1024), device=dev)
     a = model.prefill(ids, lucid=False)
-    b = model.prefill(ids, lucid=True)
+    tap = []
+    b = model.prefill(ids, lucid=True, tap=tap)
     assert torch.isfinite(a.float()).all() and torch.isfinite(b.float()).all()
     assert not torch.equal(a, b)          # the one global layer (the 6th) went through the solve
+    # the solve inside the model against the oracle on the very K/V it was handed (strided BSHD views of the
+    # model's BHSD tensors, key scale folded into the kernels)
+    from oracle import lucid_oracle as orc
+
+    assert [t[0] for t in tap] == [5]
+    _, k, v, v_prime, ks = tap[0]
+    assert not k.is_contiguous() and k.shape == (1, 1024, 4, 128)
+    ref = orc.forward_sub_blockwise(k.double() * ks, v.double())
+    assert orc.rel_err(v_prime, ref) < 0.01

@@ -93,9 +93,15 @@ def test_identity_diagonal_and_window(ops):
     Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
     out = ops._forward_sub_fwd(Kc, Vc, use_diag_solve=False, check=True)
     assert orc.rel_err(out, orc.forward_sub_blockwise(K, V, use_diag_solve=False)) < 0.01
-    for w in (1, 3):
+    # window 0 subtracts no earlier block (only the diagonal-block solve), as in the reference
+    # (min(m_block, window_size), forward_sub_fwd.py:518-519); None is full causality
+    for w in (0, 1, 3):
         out = ops._forward_sub_fwd(Kc, Vc, use_diag_solve=True, window_size=w, check=True)
         assert orc.rel_err(out, orc.forward_sub_blockwise(K, V, window_size=w)) < 0.01
+    full = ops._forward_sub_fwd(Kc, Vc, use_diag_solve=True, window_size=None, check=True)
+    assert orc.rel_err(full, orc.forward_sub_blockwise(K, V)) < 0.01
+    with pytest.raises(AssertionError):
+        ops._forward_sub_fwd(Kc, Vc, window_size=-2)
     vp = orc.forward_sub_blockwise(K, V, use_diag_solve=False).bfloat16()
     dv, dk = ops._forward_sub_bwd(Kc, vp.cuda(), Gc, use_diag_solve=False, use_combined_kernel=True, check=True)
     rdv, rdk = orc.backward_blockwise(K, vp, G, use_diag_solve=False)
@@ -323,30 +329,183 @@ def test_argument_errors(ops):
         ops._forward_sub_fwd(K, V)                                          # not on CUDA
 
 
-def test_diag_inverse_reuse_is_safe(ops):
-    """The backward after a forward on the same k object reuses the diagonal-block inverses left in the
-    workspace; a different k (even one that lands at the same address) or an in-place update must not."""
+def test_diag_inverse_reuse_is_opt_in_and_safe(ops):
+    """Bare calls recompute the diagonal-block inverses every time, like the reference.  With reuse_diag=True the
+    backward after a forward on the same k object reuses those left in the workspace; a different k (even one
+    that lands at the same address) or an in-place update must not."""
     from lucid_kernels_b200 import _cabi
 
     K, V, G = orc.make_inputs(1, 512, 2, dtype=torch.bfloat16, seed=5)
     Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
     vp = ops._forward_sub_fwd(Kc, Vc, check=True)
     stream = torch.cuda.current_stream().cuda_stream
-    ws = _cabi.workspace(Kc.device, stream, 1, 512, 2)
-    assert _cabi.diag_is_cached(ws, Kc)
-    dv_cached, dk_cached = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
-    _cabi.diag_remember(ws, Kc, False)                     # force recomputation
-    dv_fresh, dk_fresh = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+    assert _cabi.diag_is_cached(Kc.device, stream, Kc)
+    dv_cached, dk_cached = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True, reuse_diag=True)
+    dv_fresh, dk_fresh = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)   # default: recompute
     assert torch.equal(dv_cached, dv_fresh) and torch.equal(dk_cached, dk_fresh)
+    # a writer torch cannot see (raw pointer): the default path is still right, because it never trusts the cache
+    K1, _, _ = orc.make_inputs(1, 512, 2, dtype=torch.bfloat16, seed=55)
+    Kc.data.copy_(K1.cuda())           # (this one does bump the counter; the point is the default below)
+    vp1 = ops._forward_sub_fwd(Kc, Vc, check=True)
+    assert orc.rel_err(vp1, orc.forward_sub_blockwise(K1, V)) < 0.01
     # a new tensor of the same shape, possibly at the same address, is not a cache hit
     addr = Kc.data_ptr()
     del Kc
     K2, V2, _ = orc.make_inputs(1, 512, 2, dtype=torch.bfloat16, seed=6)
     K2c = K2.cuda()
-    vp2 = ops._forward_sub_fwd(K2c, V2.cuda(), check=True)
-    assert orc.rel_err(vp2, orc.forward_sub_blockwise(K2, V2)) < 0.01, (addr == K2c.data_ptr())
+    assert not _cabi.diag_is_cached(K2c.device, stream, K2c), (addr == K2c.data_ptr())
+    vp2 = ops._forward_sub_fwd(K2c, V2.cuda(), check=True, reuse_diag=True)
+    assert orc.rel_err(vp2, orc.forward_sub_blockwise(K2, V2)) < 0.01
     # an in-place update bumps the version counter
     K2c.mul_(0.5)
-    assert not _cabi.diag_is_cached(ws, K2c)
-    vp3 = ops._forward_sub_fwd(K2c, V2.cuda(), check=True)
+    assert not _cabi.diag_is_cached(K2c.device, stream, K2c)
+    vp3 = ops._forward_sub_fwd(K2c, V2.cuda(), check=True, reuse_diag=True)
     assert orc.rel_err(vp3, orc.forward_sub_blockwise(K2c.cpu(), V2)) < 0.01
+
+
+def test_dv_only_backward_with_the_diagonal_solve(ops):
+    """_forward_sub_bwd_dv(use_diag_solve=True) against the oracle and against the combined path's dV."""
+    K, V, G = orc.make_inputs(2, 1024, 3, dtype=torch.bfloat16, seed=9)
+    Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+    vp = ops._forward_sub_fwd(Kc, Vc, check=True)
+    dv_only = ops._forward_sub_bwd_dv(Kc, Gc, use_diag_solve=True, check=True)
+    dv, _ = ops._forward_sub_bwd_combined(Kc, vp, Gc, use_diag_solve=True, check=True)
+    assert torch.equal(dv_only, dv)
+    rdv, _ = orc.backward_blockwise(K, vp.cpu(), G)
+    assert orc.rel_err(dv_only, rdv) < 0.01
+
+
+def test_expanded_inputs_are_materialised_not_misread(ops):
+    """k expanded over the heads (stride 0, the GQA broadcast pattern) has no tensor map: the interface makes
+    it contiguous, and the C ABI refuses such strides outright instead of reading neighbouring rows."""
+    import ctypes
+    from lucid_kernels_b200 import _cabi
+
+    K, V, _ = orc.make_inputs(1, 512, 1, dtype=torch.bfloat16, seed=13)
+    _, V4, _ = orc.make_inputs(1, 512, 4, dtype=torch.bfloat16, seed=14)
+    Kc, V4c = K.cuda(), V4.cuda()
+    k_exp = Kc.expand(1, 512, 4, 128)
+    assert k_exp.stride(2) == 0
+    out = ops._forward_sub_fwd(k_exp, V4c, check=True)
+    ref = orc.forward_sub_blockwise(K.expand(1, 512, 4, 128), V4)
+    assert orc.rel_err(out, ref) < 0.01
+    lib = _cabi.load()
+    ws = _cabi.workspace(Kc.device, torch.cuda.current_stream().cuda_stream, 1, 512, 4)
+    res = torch.empty_like(V4c)
+    rc = lib.lucid_fwd_sub(k_exp.data_ptr(), V4c.data_ptr(), res.data_ptr(), _cabi.strides3(k_exp),
+                           _cabi.strides3(V4c), _cabi.strides3(res), 1, 512, 4, 128, 1, 1, -1, 0, ws.data_ptr(),
+                           ws.numel(), torch.cuda.current_stream().cuda_stream)
+    assert rc == -9 and b"stride" in lib.lucid_status_string(rc)
+
+
+def test_step_captured_twice_replays_with_fresh_inverses(ops):
+    """The usual static-input pattern: capture the step, later capture it again with the same K object, write
+    new values into K, replay.  Each capture works in its own workspace and recomputes the diagonal inverses
+    inside the graph, so neither replay can solve with inverses of earlier contents."""
+    K, V, G = orc.make_inputs(1, 1024, 2, dtype=torch.bfloat16, seed=61)
+    Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+
+    def step():
+        vp = ops._forward_sub_fwd(Kc, Vc)
+        dv, dk = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, reuse_diag=True)
+        return vp, dv, dk
+
+    s = torch.cuda.Stream()
+    step()                                            # an eager call first, on the current stream
+    torch.cuda.synchronize()
+    graphs, outs = [], []
+    for _ in range(2):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s, capture_error_mode="thread_local"):
+            outs.append(step())
+        graphs.append(g)
+        with torch.cuda.stream(s):
+            step()                                    # and an eager call on the capture stream in between
+        torch.cuda.synchronize()
+    K2, V2, G2 = orc.make_inputs(1, 1024, 2, dtype=torch.bfloat16, seed=62)
+    Kc.copy_(K2.cuda()); Vc.copy_(V2.cuda()); Gc.copy_(G2.cuda())
+    rvp, rdv, rdk = orc.dense_fwd_bwd(K2, V2, G2)
+    for g, out in zip(graphs, outs):
+        g.replay()
+        torch.cuda.synchronize()
+        assert orc.rel_err(out[0], rvp) < 0.01 and orc.rel_err(out[1], rdv) < 0.01 and orc.rel_err(out[2], rdk) < 0.02
+
+
+def test_two_streams_with_pairs_of_row_blocks(ops):
+    """Two forward solves of a pair-eligible shape (clusters of two CTAs) on two streams at once: neither launch
+    has the GPU to itself, so pairs must be claimed by ticket by clusters that are actually running."""
+    K, V, _ = orc.make_inputs(1, 8192, 8, dtype=torch.bfloat16, seed=71)
+    Kc, Vc = K.cuda(), V.cuda()
+    ref = ops._forward_sub_fwd(Kc, Vc, check=True)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    outs = []
+    for _ in range(3):
+        with torch.cuda.stream(s1):
+            outs.append(ops._forward_sub_fwd(Kc, Vc))
+        with torch.cuda.stream(s2):
+            outs.append(ops._forward_sub_fwd(Kc, Vc))
+    with torch.cuda.stream(s1):
+        a = ops._forward_sub_fwd(Kc, Vc, check=True)
+    with torch.cuda.stream(s2):
+        b = ops._forward_sub_fwd(Kc, Vc, check=True)
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, ref) for o in outs) and torch.equal(a, ref) and torch.equal(b, ref)
+
+
+def _oracle_one_system(K, V, G, vp, dv, dk, s):
+    """Errors of system s (index into the head dimension of (1, N, n, 128) tensors) against the fp64 block
+    recurrence, evaluated on the GPU."""
+    k1, v1, g1 = [t[:, :, s:s + 1].cuda().double() for t in (K, V, G)]
+    rvp = orc.forward_sub_blockwise(k1, v1)
+    e = [orc.rel_err(vp[:, :, s:s + 1], rvp)]
+    if dv is not None:
+        rdv, rdk = orc.backward_blockwise(k1, vp[:, :, s:s + 1].double(), g1)
+        e += [orc.rel_err(dv[:, :, s:s + 1], rdv), orc.rel_err(dk[:, :, s:s + 1], rdk)]
+    return e
+
+
+def test_config_fwd_b1_n8192_h8_against_the_oracle(ops):
+    """Forward-only configuration B=1, N=8192, H=8 (T = 64), with pairs of row-blocks (the default for this
+    shape) and with single row-blocks: every system against the fp64 recurrence."""
+    from lucid_kernels_b200 import _cabi
+
+    lib = _cabi.load()
+    K, V, _ = orc.make_inputs(1, 8192, 8, dtype=torch.bfloat16)
+    Kc, Vc = K.cuda(), V.cuda()
+    ref = orc.forward_sub_blockwise(Kc.double(), Vc.double())
+    try:
+        assert lib.lucid_query_pair_solve(1, 8192, 8) == 1
+        vp_pair = ops._forward_sub_fwd(Kc, Vc, check=True)
+        lib.lucid_set_pair_solve(0)
+        assert lib.lucid_query_pair_solve(1, 8192, 8) == 0
+        vp_single = ops._forward_sub_fwd(Kc, Vc, check=True)
+    finally:
+        lib.lucid_set_pair_limits(8, 0)
+    for h in range(8):
+        assert orc.rel_err(vp_pair[:, :, h], ref[:, :, h]) < 0.01, h
+        assert orc.rel_err(vp_single[:, :, h], ref[:, :, h]) < 0.01, h
+
+
+def test_benchmark_shape_b2_n32768_h8_against_the_oracle(ops):
+    """The benchmarked configuration itself (B=2, N=32768, H=8: 16 systems, T = 256, scheduler groups of four,
+    separate solve and dK launches): one system of every group against the fp64 recurrence on the GPU."""
+    B, N, H = 2, 32768, 8
+    K, V, G = orc.make_inputs(B, N, H, dtype=torch.bfloat16)
+    Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+    vp = ops._forward_sub_fwd(Kc, Vc, check=True)
+    dv, dk = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True, reuse_diag=True)
+    for b, h in ((0, 0), (0, 5), (1, 2), (1, 7)):          # systems 0, 5, 10, 15: one of each group of four
+        e = _oracle_one_system(K[b:b + 1], V[b:b + 1], G[b:b + 1], vp[b:b + 1], dv[b:b + 1], dk[b:b + 1], h)
+        assert e[0] < 0.01 and e[1] < 0.01 and e[2] < 0.02, (b, h, e)
+
+
+def test_config_fwd_b1_n131072_h8_against_the_oracle(ops):
+    """Long-context forward B=1, N=131072, H=8 (T = 1024): one system against the fp64 recurrence on the GPU,
+    and the instrumented call's timestamps describe every row-block."""
+    K, V, _ = orc.make_inputs(1, 131072, 8, dtype=torch.bfloat16, hb_slice=(0, 8))
+    Kc, Vc = K.cuda(), V.cuda()
+    vp, ts = ops._forward_sub_fwd(Kc, Vc, instrument=True, check=True)
+    assert ts.shape == (8, 1024, 8) and bool((ts[:, :, 2] > ts[:, :, 0]).all())
+    e = _oracle_one_system(K, V, V, vp, None, None, 6)
+    assert e[0] < 0.01, e

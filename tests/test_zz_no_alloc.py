@@ -19,7 +19,7 @@ from oracle import lucid_oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-def _static_fwd(lib, k, v, flags=1, window=0):
+def _static_fwd(lib, k, v, flags=1, window=-1):
     from lucid_kernels_b200 import _cabi
 
     B, N, H, D = k.shape
@@ -67,7 +67,7 @@ def test_static_scratch_rejects_oversized_problems():
     # claim a problem far beyond 9 MiB of scratch: must be refused before anything is launched
     out = torch.empty_like(Vc)
     rc = lib.lucid_fwd_sub_static(Kc.data_ptr(), Vc.data_ptr(), out.data_ptr(), _cabi.strides3(Kc),
-                                  _cabi.strides3(Vc), _cabi.strides3(out), 2, 32768, 8, 128, 1, 1, 0, 0,
+                                  _cabi.strides3(Vc), _cabi.strides3(out), 2, 32768, 8, 128, 1, 1, -1, 0,
                                   torch.cuda.current_stream().cuda_stream, None)
     assert rc == -8
     assert b"scratch" in lib.lucid_status_string(rc)
