@@ -106,7 +106,7 @@ class ClockSampler:
         # the samples around it (which include idle moments and read high)
         rows = ([l for (t, l) in self.lines if t0 + 0.02 <= t <= t1] or
                 [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines])
-        sm, smax, reasons = [], [], set()
+        sm, smax, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for l in rows:
             f = [x.strip() for x in l.split(",")]
@@ -117,10 +117,15 @@ class ClockSampler:
                 smax.append(float(f[2]))
             except ValueError:
                 continue
+            try:
+                power.append(float(f[3]))
+            except ValueError:
+                pass
             for name, val in zip(names, f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(smax) if smax else None,
+                    power_w=statistics.median(power) if power else None, power_w_max=max(power) if power else None,
                     reasons=sorted(reasons), samples=len(sm))
 
 
@@ -425,6 +430,8 @@ def main():
     # ---- the same steps launched call by call, carrying per-kernel events (GPU still at its loaded state) ----
     n_prof = max(2, min(args.steps, 10))
     kern_ev = [new_events() for _ in range(n_prof)]
+    for s in range(2):            # untimed: `last` keeps one step's outputs alive, so the allocator needs a second set
+        last = profiled_step(kern_ev[s], (args.warmup + s) & 1)
     barrier()
     ea, eb = mk(), mk()
     ea.record()

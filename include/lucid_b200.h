@@ -134,7 +134,9 @@ int lucid_read_status(const void* workspace, void* cuda_stream, int32_t out[8]);
 /* Human-readable name of a status word out[0] or of a negative return code. */
 const char* lucid_status_string(int code);
 
-/* Sets the time limit (nanoseconds) of every device-side wait; default 2e9. */
+/* Sets the time limit (nanoseconds) of every device-side wait; default 2e9.  The kernels look at the clock
+ * only every few hundred polls, so limits below some tens of microseconds take effect late; 0 means "do not
+ * wait": any wait not satisfied at its first poll is reported as timed out (for testing the error path). */
 void lucid_set_wait_limit_ns(uint64_t ns);
 
 /* The same two operators for keys that the caller would otherwise scale first: the operator acts on
@@ -186,6 +188,10 @@ void lucid_set_pair_solve(int max_chains);
 /* The same switch with its second limit: pairs are used with at most `max_chains` systems and at most
  * `max_row_blocks` 128-row blocks over all systems (B*H*N/128; default 768; <= 0 restores the default). */
 void lucid_set_pair_limits(int max_chains, int max_row_blocks);
+
+/* Kernel variant of the stand-alone solves: bit 0 = the S products read K_i from tensor memory instead of
+ * shared memory (two S buffers instead of three).  No counterpart in the reference. */
+void lucid_set_solve_variant(int bits);
 
 /* 1 if lucid_fwd_sub with the diagonal solve and full causality would run this problem in that pair mode
  * under the current limits, else 0 (benchmarks use it to label what they measured). */

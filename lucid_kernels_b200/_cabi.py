@@ -30,7 +30,7 @@ EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_rea
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
            "lucid_profile_next_call", "lucid_set_head_steps", "lucid_set_group_overlap", "lucid_set_dk_split", "lucid_fwd_sub_static",
            "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled",
-           "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve")
+           "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve", "lucid_set_solve_variant")
 
 
 class LucidKernelError(RuntimeError):
@@ -61,6 +61,10 @@ def load() -> ctypes.CDLL:
         lib.lucid_fwd_workspace_bytes.argtypes = [c.c_int, c.c_int, c.c_int]
         lib.lucid_stream_capture_id.restype = c.c_ulonglong
         lib.lucid_stream_capture_id.argtypes = [c.c_void_p]
+        lib.lucid_set_solve_variant.restype = None
+        lib.lucid_set_solve_variant.argtypes = [c.c_int]
+        if os.environ.get("LUCID_B200_SOLVE_VARIANT"):
+            lib.lucid_set_solve_variant(int(os.environ["LUCID_B200_SOLVE_VARIANT"]))
         lib.lucid_query_pair_solve.restype = c.c_int
         lib.lucid_query_pair_solve.argtypes = [c.c_int, c.c_int, c.c_int]
         lib.lucid_set_pair_limits.restype = None

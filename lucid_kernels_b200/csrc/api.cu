@@ -17,6 +17,7 @@ static int g_fuse_max_chains = 2;   // combined backward: fuse solve and dK into
 static int g_fuse_solve_ctas = 0;   // 0 = automatic share
 static int g_pair_max_chains = 8;   // solve pairs of row-blocks with clusters of two CTAs up to this many chains
 static int g_pair_max_blocks = 768; // ... and up to this many row-blocks in all (chains * T)
+static int g_solve_variant = 0;     // bit 0: the stand-alone solves read K_i from tensor memory
 static int g_head = -1;   // scheduler knob; < 0 = default
 static int g_overlap = -1;   // scheduler knob; < 0 = default
 static int g_dk_split = 1;   // one-launch backward: dK row-blocks as two work items
@@ -221,11 +222,12 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
       const int items = CT / 2;
       pgrid = 2 * (items < sms / 2 ? items : sms / 2);
     }
-    e = launch_solve(bf16, reverse, pair, tm_k, tm_in, tm_out, tm_x, tm_st, sa, pair ? pgrid : grid, stream);
+    const bool kt = (g_solve_variant & 1) != 0;
+    e = launch_solve(bf16, reverse, pair, kt, tm_k, tm_in, tm_out, tm_x, tm_st, sa, pair ? pgrid : grid, stream);
     if (pair && e != cudaSuccess) {
       // no room for clusters on this device (a partitioned GPU, for instance): single row-blocks always launch
       (void)cudaGetLastError();
-      e = launch_solve(bf16, reverse, false, tm_k, tm_in, tm_out, tm_x, tm_st, sa, grid, stream);
+      e = launch_solve(bf16, reverse, false, kt, tm_k, tm_in, tm_out, tm_x, tm_st, sa, grid, stream);
     }
   }
   if (e != cudaSuccess) return (int)e;
@@ -276,6 +278,8 @@ int lucid_query_pair_solve(int B, int N, int H) {
   if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
   return pair_eligible(make_problem(B, N, H, LUCID_FLAG_DIAG_SOLVE, -1, 0, 1.0f)) ? 1 : 0;
 }
+
+void lucid_set_solve_variant(int bits) { g_solve_variant = bits; }
 
 void lucid_set_pair_solve(int max_chains) { g_pair_max_chains = max_chains; }
 

@@ -62,10 +62,17 @@ __device__ __forceinline__ void report_error(Control* ctl, int code, int chain, 
 }
 
 // Wait for an mbarrier phase with a time limit.  Returns false (after flagging the CTA-wide abort
-// word) when the limit runs out or another role of this CTA has already given up.
+// word) when the limit runs out or another role of this CTA has already given up.  The clock is looked at
+// only every few hundred polls, so a limit shorter than that takes effect late; a limit of 0 is exact: a
+// wait that is not satisfied at its first poll fails at once (used by the test of this path).
 __device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, volatile int* cta_abort, Control* ctl,
                                              unsigned long long limit_ns, int chain, int row, int bar_id) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (limit_ns == 0) {      // "do not wait at all": whatever is not ready at once counts as timed out
+    *cta_abort = 1;
+    report_error(ctl, kErrBarrierTimeout, chain, row, 0, bar_id);
+    return false;
+  }
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -92,6 +99,11 @@ __device__ __forceinline__ bool wait_flag(const int* flag, volatile int* cta_abo
                                           unsigned long long limit_ns, int chain, int row, int dep_row,
                                           unsigned long long* waited) {
   if (ld_acquire_gpu(flag) >= kFlagComplete) return true;
+  if (limit_ns == 0) {
+    *cta_abort = 1;
+    report_error(ctl, kErrFlagTimeout, chain, row, dep_row, -1);
+    return false;
+  }
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   bool ok = true;

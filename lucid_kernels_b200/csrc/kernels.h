@@ -39,9 +39,10 @@ struct DkArgs {
 
 // pair = clusters of two CTAs solving pairs of consecutive row-blocks (needs an even number of row-blocks per
 // chain, the diagonal solve and full causality); grid is then rounded to whole resident clusters.
-cudaError_t launch_solve(bool bf16, bool reverse, bool pair, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
-                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const CUtensorMap& tm_st,
-                         const SolveArgs& args, int grid, cudaStream_t stream);
+// ki_in_tmem = the variant whose S products read K_i from tensor memory (two S buffers instead of three).
+cudaError_t launch_solve(bool bf16, bool reverse, bool pair, bool ki_in_tmem, const CUtensorMap& tm_k,
+                         const CUtensorMap& tm_in, const CUtensorMap& tm_out, const CUtensorMap& tm_x,
+                         const CUtensorMap& tm_st, const SolveArgs& args, int grid, cudaStream_t stream);
 cudaError_t launch_diag_prep(bool bf16, const CUtensorMap& tm_k, const PrepArgs& args, int nblocks,
                              cudaStream_t stream);
 cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,

@@ -40,6 +40,12 @@
 // the epilogue the same way.  Two issuing warps because tcgen05.mma issue is nearly synchronous
 // with execution (the queue holds only a few instructions): the waits of one overlap the MMAs of the other.
 //
+// Variant kKT ("K_i in tensor memory"): the exp groups copy K_i from shared memory into 64 TMEM columns once
+// per row-block and every S product reads its A operand from there, so a tile's S product reads 32 KiB less
+// from shared memory, whose port (128 bytes per clock: 64 KiB of tile loads landing, 96 KiB of operand
+// reads per tile) is otherwise the busiest unit of the SM.  It pays for the columns with one S buffer (two
+// instead of three).
+//
 // TMEM: three S buffers (tile g uses buffer g % 3) and the accumulator.  An exp thread streams its
 // columns of S through registers in 16-column chunks (the next chunk's load in flight) and writes the
 // packed P chunk over S columns it has already consumed, so P needs no buffer of its own and the S
@@ -58,7 +64,7 @@ struct SolveSmem {
   alignas(1024) uint8_t vring[4][kHalfBytes];  // Y_j row halves (2 panels x 64 rows x 64 columns)
   alignas(8) uint64_t k_full[4];
   uint64_t k_empty[4], v_full[4], v_empty[4];
-  uint64_t ki_full, ki_free, x_full, vi_full, xr_free, r_free, stage_full;
+  uint64_t ki_full, ki_free, x_full, vi_full, xr_free, r_free, stage_full, kit_full;
   uint64_t s_full[3], sbuf_free[3], p_full[3];
   uint64_t acc_full, acc_free, rhs_full, out_full, pq_full, q_full;
 
@@ -74,7 +80,7 @@ enum SolveBar : int {
   BAR_K_FULL = 1, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_KI_FULL, BAR_KI_FREE, BAR_X_FULL, BAR_VI_FULL,
   BAR_XR_FREE, BAR_S_FULL, BAR_P_FULL, BAR_ACC_FULL, BAR_ACC_FREE, BAR_RHS_FULL, BAR_OUT_FULL, BAR_TK_FULL,
   BAR_TK_EMPTY, BAR_S_FREE, BAR_P_FREE, BAR_R_FREE, BAR_STAGE_FULL, BAR_PQ_FULL, BAR_Q_FULL, BAR_PEER_READY,
-  BAR_PEER_TICKET
+  BAR_PEER_TICKET, BAR_KIT_FULL
 };
 
 // Block size: four service warps plus kG exp groups of four warps (128 threads, one per row).
@@ -85,6 +91,7 @@ constexpr int kSolveGroups = 4;                          // the stand-alone kern
 // same buffer) and the accumulator; the diagonal product reuses the accumulator's columns once the
 // epilogue has read them.  Tile g uses S[g % 3].
 constexpr int kTmemS = 0, kTmemAcc = 384, kTmemOut = 384;
+constexpr int kTmemKi = 256;      // variant kKT: K_i as a TMEM operand (64 columns), in place of the third S buffer
 // Register budget per thread after the role split: the exp / epilogue groups hold a whole S row (128
 // fp32) in registers, the four service warps need few.  128 * 56 + 256 * 224 = 64512 <= 65536.
 // Register budgets after the role split (setmaxnreg), for kG = 2: 128 * 72 + 256 * 216 = 64512; for kG = 4
@@ -95,7 +102,7 @@ template <> struct SolveRegs<4> { static constexpr int service = 64, exp = 104, 
 
 // The whole CTA program, callable from more than one kernel (the tensor maps must be __grid_constant__
 // parameters of the calling kernel).
-template <bool kBf16, bool kReverse, int kG, bool kPair = false>
+template <bool kBf16, bool kReverse, int kG, bool kPair = false, bool kKT = false>
 __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, box 64 x 128
                                            const CUtensorMap& tm_in,    // V (or dV'), box 64 x 128
                                            const CUtensorMap& tm_out,   // Y, box 64 x 64
@@ -112,6 +119,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
   const unsigned long long limit = P.wait_ns;
   volatile int* cta_abort = &s.abort_flag;
   constexpr int kExpThreads = 128 * kG;      // exp / epilogue threads
+  constexpr int kNS = kKT ? 2 : 3;           // S buffers in TMEM
   constexpr int kCols = 128 / kG;            // columns of a tile (and of the output) per exp group
   constexpr int kRegsService = SolveRegs<kG>::service, kRegsExp = SolveRegs<kG>::exp,
                 kRegsLaunch = SolveRegs<kG>::launch;
@@ -131,6 +139,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     // pair mode, first CTA: the staged tile is also copied to the peer, which acknowledges receipt
     mbar_init(&s.r_free, (kPair && cluster_ctarank() == 0) ? 2 : 1);
     mbar_init(&s.stage_full, kExpThreads);
+    mbar_init(&s.kit_full, kExpThreads);
     for (int i = 0; i < 3; ++i) {
       mbar_init(&s.s_full[i], 1);
       mbar_init(&s.sbuf_free[i], 1);
@@ -379,14 +388,17 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         mbar_arrive_w(&s.tk_empty[slot]);
         int chain, i, n, jfirst;
         if (!item_geometry(ticket, chain, i, n, jfirst)) break;
-        if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_KI_FULL)) break;
+        // K_i is in place: in shared memory, or (kKT) copied into tensor memory by the exp groups
+        if (kKT ? !wait_barrier(&s.kit_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_KIT_FULL)
+                : !wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_KI_FULL))
+          break;
         tc_fence_after_sync();
         if (leader) LUCID_TR(args.trace, 2, trc, 35, n);
         for (int q = 0; q < n; ++q) {
           const uint32_t gq = g + q;
-          const uint32_t buf = gq % 3;
-          // the P*Y product of three tiles ago, which read P from this buffer, has completed
-          if (!wait_barrier(&s.sbuf_free[buf], ((gq / 3) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_S_FREE)) {
+          const uint32_t buf = gq % kNS;
+          // the P*Y product of kNS tiles ago, which read P from this buffer, has completed
+          if (!wait_barrier(&s.sbuf_free[buf], ((gq / kNS) & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_S_FREE)) {
             alive = false;
             break;
           }
@@ -406,7 +418,8 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
             const uint64_t db = d_kr0 + st * (kHalfBytes >> 4);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
-              umma_ss_w(dst, da + kk * 2, db + kk * 2, idesc_s, (half | kk) ? 1u : 0u);
+              if (kKT) umma_ts_w(dst, tmem + kTmemKi + (half * 4 + kk) * 8, db + kk * 2, idesc_s, (half | kk) ? 1u : 0u);
+              else umma_ss_w(dst, da + kk * 2, db + kk * 2, idesc_s, (half | kk) ? 1u : 0u);
             }
             umma_commit_w(&s.k_empty[st]);
           }
@@ -455,8 +468,8 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         const int n_acc = via_q ? n - 1 : n;      // tiles accumulated before the diagonal product
         // ACC (or OUT, with fold) += P[buf] * Y ring tile of tile gq
         auto issue_py = [&](uint32_t gq, bool first, bool fold) -> bool {
-          const uint32_t buf = gq % 3;
-          if (!wait_barrier(&s.p_full[buf], (gq / 3) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) return false;
+          const uint32_t buf = gq % kNS;
+          if (!wait_barrier(&s.p_full[buf], (gq / kNS) & 1, cta_abort, ctl, limit, chain, i, BAR_P_FULL)) return false;
           if (leader) LUCID_TR(args.trace, 5, trc, 32, gq);
           if (first && !wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_ACC_FREE))
             return false;
@@ -503,7 +516,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           if (!wait_barrier(&s.pq_full, nq & 1, cta_abort, ctl, limit, chain, i, BAR_PQ_FULL)) break;
           if (!wait_barrier(&s.x_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_X_FULL)) break;
           tc_fence_after_sync();
-          const uint32_t q_tmem = tmem + kTmemS + ((g + n - 1) % 3) * 128;
+          const uint32_t q_tmem = tmem + kTmemS + ((g + n - 1) % kNS) * 128;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint64_t da = kReverse ? desc_advance(d_x, k * 2048)
@@ -581,11 +594,31 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
       }
       const float lam = P.use_diag ? args.lam_inv[(chain * T + i) * kBlock + row] : 1.0f;
 
+      if (kKT) {
+        // K_i, shared memory -> tensor memory: this thread's row, this group's kCols columns (kCols / 2 words of
+        // 16-bit pairs).  The region's previous reader, the last S product of the item before, completed before
+        // the load of this K_i was even issued.
+        if (!wait_barrier(&s.ki_full, it & 1, cta_abort, ctl, limit, chain, i, BAR_KI_FULL)) break;
+#pragma unroll
+        for (int c = 0; c < kCols / 32; ++c) {
+          uint32_t w[16];
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            const uint4 t4 = *reinterpret_cast<const uint4*>(my_ki + sw128_off(row, vec0 + c * 4 + v4));
+            w[4 * v4] = t4.x; w[4 * v4 + 1] = t4.y; w[4 * v4 + 2] = t4.z; w[4 * v4 + 3] = t4.w;
+          }
+          tmem_st16(lane_base + kTmemKi + wg * (kCols / 2) + c * 16, w);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&s.kit_full);
+      }
+
       // ---- P = exp(S): this group's kCols columns of every tile ----
       for (int q = 0; q < n; ++q) {
         const uint32_t gq = g + q;
-        const uint32_t buf = gq % 3;
-        const uint32_t ph = (gq / 3) & 1;
+        const uint32_t buf = gq % kNS;
+        const uint32_t ph = (gq / kNS) & 1;
         if (!wait_barrier(&s.s_full[buf], ph, cta_abort, ctl, limit, chain, i, BAR_S_FULL)) {
           alive = false;
           break;
@@ -866,12 +899,12 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
 }
 
 #ifndef LUCID_BODY_ONLY
-template <bool kBf16, bool kReverse, bool kPair>
+template <bool kBf16, bool kReverse, bool kPair, bool kKT>
 __global__ void __launch_bounds__(solve_threads(kSolveGroups), 1)
 solve_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_in,
              const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_x,
              const __grid_constant__ CUtensorMap tm_st, const SolveArgs args) {
-  solve_body<kBf16, kReverse, kSolveGroups, kPair>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
+  solve_body<kBf16, kReverse, kSolveGroups, kPair, kKT>(tm_k, tm_in, tm_out, tm_x, tm_st, args);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -879,11 +912,11 @@ solve_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ C
 // ---------------------------------------------------------------------------------------------
 size_t solve_smem_bytes() { return sizeof(SolveSmem) + 1024; }
 
-template <bool kBf16, bool kReverse, bool kPair>
+template <bool kBf16, bool kReverse, bool kPair, bool kKT>
 static cudaError_t launch_solve_t(const CUtensorMap& tm_k, const CUtensorMap& tm_in, const CUtensorMap& tm_out,
                                   const CUtensorMap& tm_x, const CUtensorMap& tm_st, const SolveArgs& args, int grid,
                                   cudaStream_t stream) {
-  auto kern = solve_kernel<kBf16, kReverse, kPair>;
+  auto kern = solve_kernel<kBf16, kReverse, kPair, kKT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)solve_smem_bytes());
   if (e != cudaSuccess) return e;
   if (!kPair) {
@@ -912,17 +945,24 @@ static cudaError_t launch_solve_t(const CUtensorMap& tm_k, const CUtensorMap& tm
   return cudaLaunchKernelEx(&cfg, kern, tm_k, tm_in, tm_out, tm_x, tm_st, args);
 }
 
-cudaError_t launch_solve(bool bf16, bool reverse, bool pair, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
-                         const CUtensorMap& tm_out, const CUtensorMap& tm_x, const CUtensorMap& tm_st,
-                         const SolveArgs& args, int grid, cudaStream_t stream) {
-#define LUCID_LAUNCH(BF, REV, PAIR) \
-  launch_solve_t<BF, REV, PAIR>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
-  if (bf16) {
-    if (pair) return reverse ? LUCID_LAUNCH(true, true, true) : LUCID_LAUNCH(true, false, true);
-    return reverse ? LUCID_LAUNCH(true, true, false) : LUCID_LAUNCH(true, false, false);
-  }
-  if (pair) return reverse ? LUCID_LAUNCH(false, true, true) : LUCID_LAUNCH(false, false, true);
-  return reverse ? LUCID_LAUNCH(false, true, false) : LUCID_LAUNCH(false, false, false);
+template <bool kBf16, bool kReverse>
+static cudaError_t launch_solve_v(bool pair, bool kt, const CUtensorMap& tm_k, const CUtensorMap& tm_in,
+                                  const CUtensorMap& tm_out, const CUtensorMap& tm_x, const CUtensorMap& tm_st,
+                                  const SolveArgs& args, int grid, cudaStream_t stream) {
+  if (pair)
+    return kt ? launch_solve_t<kBf16, kReverse, true, true>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
+              : launch_solve_t<kBf16, kReverse, true, false>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream);
+  return kt ? launch_solve_t<kBf16, kReverse, false, true>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
+            : launch_solve_t<kBf16, kReverse, false, false>(tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream);
+}
+
+cudaError_t launch_solve(bool bf16, bool reverse, bool pair, bool ki_in_tmem, const CUtensorMap& tm_k,
+                         const CUtensorMap& tm_in, const CUtensorMap& tm_out, const CUtensorMap& tm_x,
+                         const CUtensorMap& tm_st, const SolveArgs& args, int grid, cudaStream_t stream) {
+#define LUCID_LAUNCH(BF, REV) \
+  launch_solve_v<BF, REV>(pair, ki_in_tmem, tm_k, tm_in, tm_out, tm_x, tm_st, args, grid, stream)
+  if (bf16) return reverse ? LUCID_LAUNCH(true, true) : LUCID_LAUNCH(true, false);
+  return reverse ? LUCID_LAUNCH(false, true) : LUCID_LAUNCH(false, false);
 #undef LUCID_LAUNCH
 }
 #endif  // LUCID_BODY_ONLY

@@ -1,8 +1,8 @@
 """A device-side wait that runs out must end in an error status, not in a hang.
 
 Every wait in the kernels (mbarrier or flag) has a time limit (`lucid_set_wait_limit_ns`, 2 s by default).
-Here the limit is set to a few hundred nanoseconds, far below the time any tile load or hand-over takes, so
-the first wait that is not satisfied at once expires: the call must come back with a LucidKernelError that
+Here the limit is set to 0, which the kernels read as "do not wait": the first wait that is not satisfied at
+once (the first tile load, at the latest) counts as expired, in every CTA.  The call must come back with a LucidKernelError that
 names the kernel and the place, the GPU must stay usable, and a normal call on the same workspace afterwards
 must give the right answer.  Nothing is made to fault: the kernels simply give up, wait out their copies in
 flight, free their tensor memory and return.  The reference has no counterpart (its waits spin without limit,
@@ -30,7 +30,7 @@ def test_expired_wait_is_reported_and_the_next_call_is_fine():
     torch.cuda.synchronize()
     try:
         lib.lucid_set_pair_solve(0)                   # the plain one-CTA-per-row-block path
-        lib.lucid_set_wait_limit_ns(300)
+        lib.lucid_set_wait_limit_ns(0)
         with pytest.raises(LucidKernelError) as err:
             _forward_sub_fwd(Kc, Vc, check=True)
     finally:
