@@ -665,23 +665,45 @@ def main():
     ok = True
     if rank == 0:
         peaks = load_peaks()
-        # dominant kernel = the dK kernel; roofline against the measured bf16 tensor peaks
-        f_dk_local = f_dk * n_local / nsys
-        # DRAM bytes per dk_kernel launch: 254.9 MB measured by ncu at N=16384 with 16 systems, equal to the
-        # compulsory bytes (read K, V', dV; write dK), which scale with N and with the systems on this rank
-        traffic = 254.9e6 * (N / 16384.0) * (n_local / 16.0)
-        dk_exec = (T_ * (T_ + 1)) * 3 * G * n_local       # S, G and W*K for every ORDERED pair of row-blocks
+        # Roofline of the dominant kernel (the longest of the step) against the measured bf16 tensor peaks.
+        # Algorithmic flops per kernel: forward solve and reverse solve 2g per pair of blocks + 1.5g per diagonal
+        # block each; dK 3g per pair + 2g per diagonal block.  With more than two systems per GPU the reverse solve
+        # also accumulates the upper-triangle dK terms (kernel revdk), and the dK kernel runs the lower part: each
+        # of the two is then credited half of dK's pair flops.  Executed flops: 2g per pair in a solve, 3g per
+        # ORDERED pair handled by the dK kernel, 2g more per pair in revdk.
+        pairs_local = n_local * T_ * (T_ - 1) / 2
+        diag_local = n_local * T_
         fused = k_ms["bwd_dk"] < 0.05 * k_ms["bwd_solve"]
+        upper_in_solve = (not fused) and bool(lib.lucid_query_upper_in_solve(1, N, n_local))
+        kern = {}
+        kern["solve_kernel (forward)"] = dict(ms=k_ms["fwd_solve"], algo=pairs_local * 2 * G + diag_local * 1.5 * G,
+                                              executed=pairs_local * 2 * G + diag_local * 3 * G)
         if fused:
-            # one or two systems per GPU: the library ran the reverse solve and dK in ONE launch (timed here
-            # as bwd_solve); the dominant kernel is then that launch, with the flops of both programs
-            dom_kernel = "bwd_fused_kernel (reverse solve + dK in one launch)"
-            t_dom = (k_ms["bwd_solve"] + k_ms["bwd_dk"]) * 1e-3
-            f_dom = (f_dk + f_rev) * n_local / nsys
-            exec_dom = dk_exec + f_rev * n_local / nsys
+            # one or two systems per GPU: the library ran the reverse solve and dK in ONE launch (timed as bwd_solve)
+            kern["bwd_fused_kernel (reverse solve + dK in one launch)"] = dict(
+                ms=k_ms["bwd_solve"] + k_ms["bwd_dk"], algo=pairs_local * 5 * G + diag_local * 3.5 * G,
+                executed=pairs_local * 8 * G + diag_local * 9 * G)
+        elif upper_in_solve:
+            kern["revdk_kernel (reverse solve + upper-triangle dK)"] = dict(
+                ms=k_ms["bwd_solve"], algo=pairs_local * 3.5 * G + diag_local * 1.5 * G,
+                executed=pairs_local * 4 * G + diag_local * 3 * G)
+            kern["dk_kernel (lower part, diagonal tiles, first upper tile)"] = dict(
+                ms=k_ms["bwd_dk"], algo=pairs_local * 1.5 * G + diag_local * 2 * G,
+                executed=pairs_local * 3 * G + diag_local * 9 * G)
         else:
-            dom_kernel, t_dom, f_dom, exec_dom = "dk_kernel", k_ms["bwd_dk"] * 1e-3, f_dk_local, dk_exec
-        dom_tflops = f_dom / t_dom / 1e12
+            kern["solve_kernel (reverse)"] = dict(ms=k_ms["bwd_solve"], algo=pairs_local * 2 * G + diag_local * 1.5 * G,
+                                                  executed=pairs_local * 2 * G + diag_local * 3 * G)
+            kern["dk_kernel"] = dict(ms=k_ms["bwd_dk"], algo=pairs_local * 3 * G + diag_local * 2 * G,
+                                     executed=pairs_local * 6 * G + diag_local * 6 * G)
+        for v in kern.values():
+            v["tflops"] = v["algo"] / (v["ms"] * 1e-3) / 1e12
+            v["executed_tflops"] = v["executed"] / (v["ms"] * 1e-3) / 1e12
+        dom_kernel = max(kern, key=lambda name: kern[name]["ms"])
+        dom_tflops = kern[dom_kernel]["tflops"]
+        # DRAM bytes per launch of the dominant kernel: its compulsory bytes (every ncu capture of these kernels
+        # on L2-sized scheduler groups showed DRAM traffic within 10 % of them): tensors of n_local * N * 256 bytes
+        tensor_bytes = n_local * N * 256.0
+        traffic = tensor_bytes * (3 if dom_kernel.startswith("solve") else 4 if dom_kernel.startswith("dk_kernel") else 5)
         # The burst peak is the denominator unless the kernels ran at the clock of the sustained measurement
         mhz = clocks.get("sm_mhz_in_kernel")
         at_sustained = bool(mhz and peaks["sustained_sm_mhz"] and abs(mhz / peaks["sustained_sm_mhz"] - 1.0) < 0.05)
@@ -690,15 +712,9 @@ def main():
                         frac=dom_tflops / peak, frac_burst=dom_tflops / peaks["bf16_tflops"],
                         frac_sustained=dom_tflops / peaks["bf16_tflops_sustained"], traffic=traffic,
                         peak_source=peaks["source"] + (" (sustained: kernels ran at its clock)" if at_sustained else " (burst)"),
-                        per_kernel_ms=k_ms,
-                        # The dK program forms W for every ordered pair (6 g per unordered pair, against the 3 g
-                        # the algorithmic count allows), so the tensor pipe executes about twice `achieved`.
-                        executed_tflops=exec_dom / t_dom / 1e12,
-                        per_kernel_tflops=dict(
-                            fwd_solve=f_fwd * n_local / nsys / (k_ms["fwd_solve"] * 1e-3) / 1e12,
-                            bwd_solve=None if fused else f_rev * n_local / nsys / (k_ms["bwd_solve"] * 1e-3) / 1e12,
-                            bwd_dk=None if fused else dom_tflops,
-                            bwd_fused=dom_tflops if fused else None))
+                        per_kernel_ms=k_ms, executed_tflops=kern[dom_kernel]["executed_tflops"],
+                        per_kernel={name: dict(ms=v["ms"], tflops=v["tflops"], executed_tflops=v["executed_tflops"])
+                                    for name, v in kern.items()})
         # Bounds asked for by the metric: the tensor roofline of the algorithmic flops on this many GPUs and
         # the critical path of the two solves - T - 1 hand-overs each at the median chain step measured in THIS
         # run by the instrumented forward (in pair mode the two kinds of hand-over separately); the fraction

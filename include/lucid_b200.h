@@ -58,9 +58,10 @@ extern "C" {
 
 /* Bytes of scratch the calls below need for a (B, N, H, 128) problem.  The workspace holds the
  * inter-block flags, the scheduler's control words, the per-block unit-triangular inverses
- * (B*H*N*128 16-bit values) and their row scales, and for B*H <= 2 the fp32 partial sums of dK that the
- * one-launch backward exchanges between work items (64 KiB per 128 rows; a call given less than this, but
- * enough for the rest, runs without them).  Replaces the per-call torch.zeros / torch.empty
+ * (B*H*N*128 16-bit values) and their row scales, and 64 KiB of fp32 dK partial sums per 128 rows (the sums
+ * the one-launch backward exchanges between work items, or the upper-triangle sums the reverse solve hands to
+ * the dK kernel; a call given less than this, but at least lucid_fwd_workspace_bytes(), runs the variants that
+ * do not need them).  Replaces the per-call torch.zeros / torch.empty
  * allocations of forward_sub_interface.py:97-103,217-219,297-300 and the diag_inv tensor of :109-117. */
 size_t lucid_workspace_bytes(int B, int N, int H);
 
@@ -188,6 +189,16 @@ void lucid_set_pair_solve(int max_chains);
 /* The same switch with its second limit: pairs are used with at most `max_chains` systems and at most
  * `max_row_blocks` 128-row blocks over all systems (B*H*N/128; default 768; <= 0 restores the default). */
 void lucid_set_pair_limits(int max_chains, int max_row_blocks);
+
+/* Combined backward with more systems than the one-launch limit: the reverse solve also accumulates the
+ * upper-triangle dK terms of the tiles it streams, as Phase 1 of the reference's BackwardSubSm90 does
+ * (forward_sub_bwd.py:1113-1195), and the dK kernel runs the rest (on = 1, default); 0 = the reverse solve and
+ * a dK kernel over all tiles.  Needs the full workspace of lucid_workspace_bytes(). */
+void lucid_set_upper_in_solve(int on);
+
+/* 1 if a combined backward (diagonal solve, full workspace) of this problem would run that way under the current
+ * settings on the current device, else 0 (benchmarks use it to label what they measured). */
+int lucid_query_upper_in_solve(int B, int N, int H);
 
 /* Kernel variant of the stand-alone solves: bit 0 = the S products read K_i from tensor memory instead of
  * shared memory (two S buffers instead of three).  No counterpart in the reference. */

@@ -30,7 +30,7 @@ EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_rea
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
            "lucid_profile_next_call", "lucid_set_head_steps", "lucid_set_group_overlap", "lucid_set_dk_split", "lucid_fwd_sub_static",
            "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled",
-           "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve", "lucid_set_solve_variant")
+           "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve", "lucid_set_solve_variant", "lucid_set_upper_in_solve", "lucid_query_upper_in_solve")
 
 
 class LucidKernelError(RuntimeError):
@@ -65,6 +65,12 @@ def load() -> ctypes.CDLL:
         lib.lucid_set_solve_variant.argtypes = [c.c_int]
         if os.environ.get("LUCID_B200_SOLVE_VARIANT"):
             lib.lucid_set_solve_variant(int(os.environ["LUCID_B200_SOLVE_VARIANT"]))
+        lib.lucid_query_upper_in_solve.restype = c.c_int
+        lib.lucid_query_upper_in_solve.argtypes = [c.c_int, c.c_int, c.c_int]
+        lib.lucid_set_upper_in_solve.restype = None
+        lib.lucid_set_upper_in_solve.argtypes = [c.c_int]
+        if os.environ.get("LUCID_B200_UPPER_IN_SOLVE"):
+            lib.lucid_set_upper_in_solve(int(os.environ["LUCID_B200_UPPER_IN_SOLVE"]))
         lib.lucid_query_pair_solve.restype = c.c_int
         lib.lucid_query_pair_solve.argtypes = [c.c_int, c.c_int, c.c_int]
         lib.lucid_set_pair_limits.restype = None
@@ -158,26 +164,28 @@ _workspaces: Dict[Tuple[int, int, int, int, int, int], _Workspace] = {}
 _MAX_WORKSPACES = 64
 
 
-def _entry(device: torch.device, stream_ptr: int, B: int, N: int, H: int) -> _Workspace:
+def _entry(device: torch.device, stream_ptr: int, B: int, N: int, H: int, full: bool = True) -> _Workspace:
+    """`full`: with the dK partial sums of the combined backward (64 KiB per 128 rows); a forward call asks for
+    the forward's share only, and a workspace grown later for a backward call replaces it."""
     lib = load()
     cap = int(lib.lucid_stream_capture_id(stream_ptr))
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr, cap, B, N, H)
     ent = _workspaces.get(key)
-    if ent is None:
-        nbytes = lib.lucid_workspace_bytes(B, N, H)
+    nbytes = lib.lucid_workspace_bytes(B, N, H) if full else lib.lucid_fwd_workspace_bytes(B, N, H)
+    if ent is None or ent.buf.numel() < nbytes:
         # torch's caching allocator hands out 512-byte aligned blocks; over-allocate to reach 1 KiB
         raw = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
         off = (-raw.data_ptr()) % 1024
-        ent = _Workspace(raw[off:off + nbytes])
-        if len(_workspaces) >= _MAX_WORKSPACES:
+        if ent is None and len(_workspaces) >= _MAX_WORKSPACES:
             # drop the oldest entry only (dict order = insertion order), with what it remembered
             _workspaces.pop(next(iter(_workspaces)))
+        ent = _Workspace(raw[off:off + nbytes])
         _workspaces[key] = ent
     return ent
 
 
-def workspace(device: torch.device, stream_ptr: int, B: int, N: int, H: int) -> torch.Tensor:
-    return _entry(device, stream_ptr, B, N, H).buf
+def workspace(device: torch.device, stream_ptr: int, B: int, N: int, H: int, full: bool = True) -> torch.Tensor:
+    return _entry(device, stream_ptr, B, N, H, full).buf
 
 
 # The inverses depend on k only, so a backward call that follows the forward call on the same k can skip
@@ -192,13 +200,13 @@ def _diag_key(k: torch.Tensor) -> tuple:
 
 def diag_is_cached(device: torch.device, stream_ptr: int, k: torch.Tensor, k_scale: float = 1.0) -> bool:
     B, N, H, _ = k.shape
-    entry = _entry(device, stream_ptr, B, N, H).diag
+    entry = _entry(device, stream_ptr, B, N, H, full=False).diag
     return entry is not None and entry[0]() is k and entry[1] == (_diag_key(k), float(k_scale))
 
 
 def diag_remember(device: torch.device, stream_ptr: int, k: torch.Tensor, valid: bool, k_scale: float = 1.0) -> None:
     B, N, H, _ = k.shape
-    ent = _entry(device, stream_ptr, B, N, H)
+    ent = _entry(device, stream_ptr, B, N, H, full=False)
     ent.diag = (weakref.ref(k), (_diag_key(k), float(k_scale))) if valid else None
 
 

@@ -18,6 +18,7 @@ static int g_fuse_solve_ctas = 0;   // 0 = automatic share
 static int g_pair_max_chains = 8;   // solve pairs of row-blocks with clusters of two CTAs up to this many chains
 static int g_pair_max_blocks = 768; // ... and up to this many row-blocks in all (chains * T)
 static int g_solve_variant = 0;     // bit 0: the stand-alone solves read K_i from tensor memory
+static int g_upper_in_solve = 1;    // combined backward: the reverse solve also accumulates the upper-triangle dK
 static int g_head = -1;   // scheduler knob; < 0 = default
 static int g_overlap = -1;   // scheduler knob; < 0 = default
 static int g_dk_split = 1;   // one-launch backward: dK row-blocks as two work items
@@ -32,6 +33,8 @@ static inline void record_event(int i, cudaStream_t stream) {
 //   X                   C*T tiles of 32 KiB (1 KiB aligned)
 //   lam_inv             C*T*128 fp32
 //   timestamps          C*T*8 int64
+//   partial             C*T*128*128 fp32 (combined backward only; a call given a workspace without it runs the
+//                       variants that do not need it)
 struct Layout {
   size_t flags, dksync, x, lam, ts, partial, need, total;   // need: without the dK partial sums
 };
@@ -48,8 +51,11 @@ static Layout make_layout(int B, int N, int H) {
   l.lam = l.x + CT * kTileBytes;
   l.ts = align_up(l.lam + CT * kBlock * 4, 256);
   l.need = l.ts + CT * 8 * 8;
+  // One fp32 128 x 128 tile per row-block: with one or two chains the partial sums of dK work items split in two
+  // (one-launch backward), with more chains the upper-triangle dK sums that the reverse solve accumulates for
+  // the dK kernel.  Never both.
   l.partial = align_up(l.need, 1024);
-  l.total = l.partial + ((size_t)B * H <= kSplitMaxChains ? CT * (size_t)kBlock * kBlock * 4 : 0);
+  l.total = l.partial + CT * (size_t)kBlock * kBlock * 4;
   return l;
 }
 
@@ -161,10 +167,16 @@ struct FusedDk {
   int n_solve;
 };
 
+// What the combined backward hands to run_solve when the reverse solve is to accumulate the upper-triangle dK.
+struct UpperPlan {
+  CUtensorMap tm_vp;
+  float* upper;
+};
+
 // shared by forward and backward: prep (if diag) + one solve (+ the dK program in the same launch)
 static int run_solve(bool reverse, const void* k, const void* in, void* out, const int64_t ks[3],
                      const int64_t ins[3], const int64_t outs[3], const Problem& p, bool bf16, uint8_t* ws,
-                     const Layout& lay, cudaStream_t stream, FusedDk* fused = nullptr) {
+                     const Layout& lay, cudaStream_t stream, FusedDk* fused = nullptr, UpperPlan* upper = nullptr) {
   const int CT = p.C * p.T;
   Control* ctl = reinterpret_cast<Control*>(ws);
   CUtensorMap tm_k, tm_in, tm_out, tm_x, tm_st;
@@ -204,7 +216,16 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
   const int sms = sm_count();
   if (sms <= 0) return LUCID_E_NO_DEVICE;
   const int grid = CT < sms ? CT : sms;
-  if (fused) {
+  if (upper) {
+    RevDkArgs ra;
+    ra.out = out;
+    ra.lam_inv = sa.lam_inv;
+    ra.flags = sa.flags;
+    ra.ctl = sa.ctl;
+    ra.upper = upper->upper;
+    ra.p = p;
+    e = launch_revdk(bf16, tm_k, tm_in, tm_st, upper->tm_vp, tm_x, ra, grid, stream);
+  } else if (fused) {
     fused->args.follow_flags = sa.flags;
     fused->args.follow_ctl = sa.ctl;
     e = launch_bwd_fused(bf16, tm_k, tm_in, tm_out, tm_x, tm_st, fused->tm_vp, fused->tm_dv, sa, fused->args,
@@ -280,6 +301,15 @@ int lucid_query_pair_solve(int B, int N, int H) {
 }
 
 void lucid_set_solve_variant(int bits) { g_solve_variant = bits; }
+
+void lucid_set_upper_in_solve(int on) { g_upper_in_solve = on; }
+
+int lucid_query_upper_in_solve(int B, int N, int H) {
+  if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
+  const int C = B * H, CT = C * (N / kBlock), sms = sm_count();
+  const bool fuse = C <= g_fuse_max_chains && sms > 0 && CT >= 2 * sms;
+  return (!fuse && g_upper_in_solve) ? 1 : 0;
+}
 
 void lucid_set_pair_solve(int max_chains) { g_pair_max_chains = max_chains; }
 
@@ -429,6 +459,8 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
     fd.args.split = 0;
     fd.args.partial = reinterpret_cast<float*>(ws + lay.partial);
     fd.args.sync = reinterpret_cast<int*>(ws + lay.dksync);
+    fd.args.lower_only = 0;
+    fd.args.upper = nullptr;
     fd.args.p = p;
   }
   // With one or two chains the reverse solve is bound by its chain latency and leaves SMs idle: the dK
@@ -445,8 +477,20 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
   // In that launch a row-block of dK (0.31 ms at N=32768) is the unit in which the launch ends; two half items
   // per row-block halve it.
   if (fuse && g_dk_split && p.C <= kSplitMaxChains && workspace_bytes >= lay.total) fd.args.split = 1;
+  // More chains than that: the reverse solve streams K_j and dV_j and forms exp(S) for every later block anyway,
+  // so it also accumulates the upper-triangle dK terms of those tiles (two more products per tile) and the dK
+  // kernel that follows runs only the lower part, the diagonal tiles and the first upper tile of every row-block.
+  UpperPlan up;
+  const bool upper_in_solve = mode == LUCID_BWD_COMBINED && !fuse && g_upper_in_solve && p.use_diag && !p.instrument &&
+                              !p.no_sync && workspace_bytes >= lay.total;
+  if (upper_in_solve) {
+    up.tm_vp = fd.tm_vp;
+    up.upper = reinterpret_cast<float*>(ws + lay.partial);
+    fd.args.lower_only = 1;
+    fd.args.upper = up.upper;
+  }
   rc = run_solve(true, k, dv_prime, dv, k_strides, dvp_strides, dv_strides, p, bf16, ws, lay, stream,
-                 fuse ? &fd : nullptr);
+                 fuse ? &fd : nullptr, upper_in_solve ? &up : nullptr);
   cudaEvent_t ev_dk = g_events[3];
   memset(g_events, 0, sizeof(g_events));
   if (rc) return rc;

@@ -22,6 +22,10 @@
 // w = -exp(s) * g in one pass, and writes the packed chunk over S columns it has already consumed.
 // S(q+1) reuses the buffer W(q-1) sat in and is issued as soon as that product has completed.
 //
+// With args.lower_only an item ends after the first upper tile (j = i + 1): the remaining upper tiles were
+// accumulated, unscaled and in fp32, by the reverse solve that also streams their operands (rev_dk.cu), and the
+// epilogue adds those sums.
+//
 // Work items: a whole row-block, or (args.split, used by the one-launch backward with one or two chains,
 // where the launch would otherwise end in units of a whole row-block) half of its tiles; the two halves
 // meet in the epilogue through fp32 sums in the workspace.
@@ -121,7 +125,8 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
   // With args.split a row-block's tiles are dealt out as two work items, tiles [q0, q1) each; the item that
   // finishes second adds the other's partial sums (see the epilogue).
   auto item_geometry = [&](int ticket, int& chain, int& i, int& n_low, int& q0, int& q1) -> bool {
-    return dk_item(ticket, P.C, T, args.follow_flags != nullptr, args.split != 0, diag_tiles, chain, i, n_low, q0, q1);
+    return dk_item(ticket, P.C, T, args.follow_flags != nullptr, args.split != 0, diag_tiles, chain, i, n_low, q0, q1,
+                   args.lower_only != 0);
   };
 
   if (warp == 0) {
@@ -476,6 +481,18 @@ __device__ __forceinline__ void dk_body(const CUtensorMap& tm_k,    // K,   box 
           for (int c = 0; c < 8; ++c)
             *reinterpret_cast<uint4*>(part_row + cc * 32 + c * 4) = make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
           continue;
+        }
+        if (args.lower_only) {
+          // the upper tiles j >= i + 2 were accumulated by the reverse solve that ran before this launch
+          const float* up = args.upper + ((long long)rb * kBlock + row) * kBlock + wg * 64 + cc * 32;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(up + c * 4));
+            v[c * 4] = __float_as_uint(__uint_as_float(v[c * 4]) + o.x);
+            v[c * 4 + 1] = __float_as_uint(__uint_as_float(v[c * 4 + 1]) + o.y);
+            v[c * 4 + 2] = __float_as_uint(__uint_as_float(v[c * 4 + 2]) + o.z);
+            v[c * 4 + 3] = __float_as_uint(__uint_as_float(v[c * 4 + 3]) + o.w);
+          }
         }
         if (order == 1) {
 #pragma unroll

@@ -34,6 +34,18 @@ struct DkArgs {
   int split;                // 1: a row-block's tiles are two work items whose sums meet through `partial`
   float* partial;           // (C*T, 128, 128) fp32 sums of the half that finished first (split only)
   int* sync;                // (2, C*T) zeroed: claim counters, then completion flags (split only)
+  int lower_only;           // 1: items end after the first upper tile; `upper` holds the rest of the upper part
+  const float* upper;       // (C*T, 128, 128) fp32 sums over the upper tiles j >= i + 2, written by revdk_kernel
+  Problem p;
+};
+
+// Reverse solve that also accumulates the upper-triangle dK terms of the tiles it streams (see rev_dk.cu).
+struct RevDkArgs {
+  void* out;                // dV, streamed back through tm_dv
+  const float* lam_inv;     // (C, T, 128)
+  int* flags;               // (C, T)
+  Control* ctl;
+  float* upper;             // (C*T, 128, 128) fp32: sum over j >= i + 2 of W_ij K_j, unscaled
   Problem p;
 };
 
@@ -45,6 +57,11 @@ cudaError_t launch_solve(bool bf16, bool reverse, bool pair, bool ki_in_tmem, co
                          const CUtensorMap& tm_st, const SolveArgs& args, int grid, cudaStream_t stream);
 cudaError_t launch_diag_prep(bool bf16, const CUtensorMap& tm_k, const PrepArgs& args, int nblocks,
                              cudaStream_t stream);
+// tm_dvp: dV' (box 64 x 128); tm_dv: dV (box 64 x 128, loads of published row-blocks and the store);
+// tm_vp: V' (box 64 x 128); tm_x: the X workspace (2D).
+cudaError_t launch_revdk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_dvp, const CUtensorMap& tm_dv,
+                         const CUtensorMap& tm_vp, const CUtensorMap& tm_x, const RevDkArgs& args, int grid,
+                         cudaStream_t stream);
 cudaError_t launch_dk(bool bf16, const CUtensorMap& tm_k, const CUtensorMap& tm_vp, const CUtensorMap& tm_dv,
                       const DkArgs& args, int grid, cudaStream_t stream);
 // Reverse solve (the first n_solve CTAs to start, counted in *arrivals, which must be zero at launch) and dK

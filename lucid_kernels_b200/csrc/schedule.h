@@ -78,16 +78,20 @@ LUCID_HD bool decode_ticket(int t, int C, int T, int group, int head, int overla
 // on) and the upper part j = i+1 .. T-1.  n_low = number of tiles that use dV_i.  An item covers tiles
 // [q0, q1): all of them, or with `split` one half each for two consecutive tickets.  In `follow` order the
 // row-blocks come last one first, step-major over the chains (the order in which the reverse solve of the
-// same launch publishes them); otherwise chain-major.
+// same launch publishes them); otherwise chain-major.  With `lower_only` the item ends after the first upper tile.
 // ---------------------------------------------------------------------------------------------
 LUCID_HD bool dk_item(int ticket, int C, int T, bool follow, bool split, bool diag_tiles, int& chain, int& i,
-                      int& n_low, int& q0, int& q1) {
+                      int& n_low, int& q0, int& q1, bool lower_only = false) {
   const int half = split ? (ticket & 1) : 0;
   if (split) ticket >>= 1;
   if (ticket < 0 || ticket >= C * T) return false;
   if (follow) {
     chain = ticket % C;
     i = T - 1 - ticket / C;
+  } else if (lower_only) {
+    // items shrink with i here: the longest row-blocks of a chain go first, so that the launch ends on short ones
+    chain = ticket / T;
+    i = T - 1 - ticket % T;
   } else {
     chain = ticket / T;
     i = ticket % T;
@@ -96,6 +100,9 @@ LUCID_HD bool dk_item(int ticket, int C, int T, bool follow, bool split, bool di
   const int n = T - 1 + (diag_tiles ? 2 : 0);
   q0 = 0;
   q1 = n;
+  // `lower_only` (needs diag_tiles, no split): the lower part, the two diagonal tiles and the first upper tile
+  // (j = i + 1); the rest of the upper part is accumulated by the reverse solve that ran before.
+  if (lower_only) q1 = imin(n, n_low + 2);
   if (split) {
     if (half) q0 = n >> 1;
     else q1 = n >> 1;

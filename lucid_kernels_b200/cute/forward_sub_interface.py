@@ -110,7 +110,7 @@ def _forward_sub_fwd(
     v_prime = torch.empty_like(v, memory_format=torch.contiguous_format)
     stream = torch.cuda.current_stream(k.device).cuda_stream
     with torch.cuda.device(k.device):
-        ws = _cabi.workspace(k.device, stream, B, N, H)
+        ws = _cabi.workspace(k.device, stream, B, N, H, full=False)
         flags = ((_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_NO_SYNC if no_sync else 0) |
                  (_cabi.FLAG_INSTRUMENT if instrument else 0))
         if window_size is not None:
@@ -143,7 +143,7 @@ def _bwd_call(k, v_prime, dv_prime, mode, use_diag_solve, instrument, check, cha
     dk = torch.empty_like(k, memory_format=torch.contiguous_format) if mode == _cabi.BWD_COMBINED else None
     stream = torch.cuda.current_stream(k.device).cuda_stream
     with torch.cuda.device(k.device):
-        ws = _cabi.workspace(k.device, stream, B, N, H)
+        ws = _cabi.workspace(k.device, stream, B, N, H, full=mode == _cabi.BWD_COMBINED)
         flags = (_cabi.FLAG_DIAG_SOLVE if use_diag_solve else 0) | (_cabi.FLAG_INSTRUMENT if instrument else 0)
         if use_diag_solve and (_REUSE_DIAG if reuse_diag is None else reuse_diag) and \
                 _cabi.diag_is_cached(k.device, stream, k_in, k_scale):

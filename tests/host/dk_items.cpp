@@ -57,8 +57,51 @@ static int check(int C, int T, bool follow, bool split, bool diag) {
   return 0;
 }
 
+// lower_only items (diagonal tiles on, no split, chain-major): every row-block once, the longest first inside a
+// chain, tiles 0 .. min(n, n_low + 2) - 1 (lower part, D1, D2, the first upper tile), A buffer balanced.
+static int check_lower_only(int C, int T) {
+  const int n = T + 1;
+  std::vector<int> items(C * T, 0);
+  int last_chain = -1, last_i = T;
+  for (int t = 0; t < C * T; ++t) {
+    int chain, i, n_low, q0, q1;
+    if (!lucid::dk_item(t, C, T, false, false, true, chain, i, n_low, q0, q1, true)) return 21;
+    if (chain < 0 || chain >= C || i < 0 || i >= T) return 22;
+    if (chain != last_chain) { last_chain = chain; last_i = T; }
+    if (i != last_i - 1) return 23;             // T-1, T-2, ... 0 inside a chain
+    last_i = i;
+    ++items[chain * T + i];
+    if (n_low != i + 1 || q0 != 0 || q1 != (i + 3 < n ? i + 3 : n)) return 24;
+    int loads = 1, waits = 0, frees = 0;
+    bool holds_dv = lucid::dk_first_a_is_dv(q0, n_low), valid = true;
+    for (int q = q0; q < q1; ++q) {
+      if (lucid::dk_reloads_a_at(q, q0, n_low)) {
+        if (valid) return 25;
+        ++loads; holds_dv = false; valid = true;
+      }
+      if (lucid::dk_waits_a_at(q, q0, n_low)) ++waits;
+      if (!valid || holds_dv != (q < n_low)) return 26;
+      const int j = lucid::dk_tile_j(n_low, q, true);
+      if (j != (q < n_low ? q : q - 1) || j > i + 1 || j >= T) return 27;
+      if (lucid::dk_frees_a_after(q, q0, q1, n_low)) { ++frees; valid = false; }
+    }
+    if (loads != waits || loads != frees || valid) return 28;
+  }
+  for (int r = 0; r < C * T; ++r) if (items[r] != 1) return 29;
+  return 0;
+}
+
 int main() {
   int cases = 0;
+  for (int C = 1; C <= 3; ++C)
+    for (int T = 1; T <= 40; ++T) {
+      const int rc = check_lower_only(C, T);
+      if (rc) {
+        std::printf("FAIL lower_only C=%d T=%d code %d\n", C, T, rc);
+        return 1;
+      }
+      ++cases;
+    }
   for (int C = 1; C <= 3; ++C)
     for (int T = 1; T <= 40; ++T)
       for (int m = 0; m < 8; ++m) {

@@ -35,10 +35,14 @@ def test_workspace_size_and_status_strings(lib):
     assert lib.lucid_workspace_bytes(1, 100, 1) == 0
     small = lib.lucid_workspace_bytes(1, 128, 1)
     big = lib.lucid_workspace_bytes(2, 32768, 8)
-    # one tile of inverses plus the fp32 dK partial sums that one or two systems may use (64 KiB per row-block)
+    # per 128 rows: one tile of inverses, flags and row scales (the forward's share), plus one fp32 tile of dK
+    # partial sums for the combined backward
     assert 32768 + 65536 < small < 65536 + 65536
-    assert lib.lucid_workspace_bytes(1, 128, 3) < 3 * 65536        # three systems: no partial sums
-    assert 128 * 2 ** 20 < big < 140 * 2 ** 20
+    assert 32768 < lib.lucid_fwd_workspace_bytes(1, 128, 1) < 40000
+    assert lib.lucid_fwd_workspace_bytes(1, 100, 1) == 0
+    assert 128 * 2 ** 20 < lib.lucid_fwd_workspace_bytes(2, 32768, 8) < 140 * 2 ** 20
+    assert big - lib.lucid_fwd_workspace_bytes(2, 32768, 8) >= 256 * 2 ** 20
+    assert big < 400 * 2 ** 20
     assert lib.lucid_status_string(0) == b"ok"
     assert b"128" in lib.lucid_status_string(-1)
     assert b"published" in lib.lucid_status_string(2)

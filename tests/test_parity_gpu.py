@@ -453,6 +453,34 @@ def test_two_streams_with_pairs_of_row_blocks(ops):
     assert all(torch.equal(o, ref) for o in outs) and torch.equal(a, ref) and torch.equal(b, ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_upper_dk_accumulated_by_the_reverse_solve(ops, dtype):
+    """With more than two systems the reverse solve also accumulates the upper-triangle dK terms of the tiles it
+    streams and the dK kernel runs the rest.  Against the plain pair of kernels (reverse solve, dK over all
+    tiles): dV bit-identical (same products in the same order), dK equal to rounding (the same terms summed in
+    two fp32 pieces), both within the gates of the oracle; T = 1, 2, 3 exercise the row-blocks without full tiles."""
+    from lucid_kernels_b200 import _cabi
+
+    lib = _cabi.load()
+    for B, N, H in ((1, 128, 3), (1, 256, 3), (1, 384, 3), (1, 1024, 3), (2, 2048, 8)):
+        K, V, G = orc.make_inputs(B, N, H, dtype=dtype, seed=17)
+        Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
+        vp = ops._forward_sub_fwd(Kc, Vc, check=True)
+        try:
+            lib.lucid_set_upper_in_solve(0)
+            dv0, dk0 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+            lib.lucid_set_upper_in_solve(1)
+            dv1, dk1 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+            dv2, dk2 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
+        finally:
+            lib.lucid_set_upper_in_solve(1)
+        assert torch.equal(dv0, dv1), (B, N, H)
+        assert torch.equal(dv1, dv2) and torch.equal(dk1, dk2), (B, N, H)
+        assert float((dk1.float() - dk0.float()).norm() / dk0.float().norm()) < 3e-3, (B, N, H)
+        rdv, rdk = orc.backward_blockwise(Kc.double(), vp.double(), Gc.double())
+        assert orc.rel_err(dv1, rdv) < 0.01 and orc.rel_err(dk1, rdk) < 0.02, (B, N, H)
+
+
 def _oracle_one_system(K, V, G, vp, dv, dk, s):
     """Errors of system s (index into the head dimension of (1, N, n, 128) tensors) against the fp64 block
     recurrence, evaluated on the GPU."""
