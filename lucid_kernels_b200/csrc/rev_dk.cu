@@ -12,14 +12,15 @@
 // kernel, which then runs the lower part, the two diagonal tiles and that one upper tile per row-block
 // (DkArgs::lower_only) and adds the fp32 sums this kernel leaves in the workspace.
 //
-// TMEM (512 columns): S (P packed in place), G (W packed in place), ACC_dV (reused for the diagonal product
-// and the closing product), ACC_dK.  S and G are single buffers, so a tile is a chain S -> exp -> products
-// that read P and W -> next S, and the kernel shortens that chain instead of hiding it: ONE warp issues every
-// tensor-core product, in program order (the tensor pipe executes one thread's products in order, so the next
-// tile's S and G may be queued right behind the products that still read P and W, with no barrier round trip
-// in between); the exp groups start on S while G is still being computed; and they work through a tile in two
-// rounds of four 16-column k-steps, the P dV_j / W K_j products of the first round running while the second
-// round is formed.
+// TMEM (512 columns): region B holds S (and, for the newest predecessor, Q), region A holds G and then the
+// packed W and P of the same tile, then ACC_dV (reused for the diagonal product and the closing product) and
+// ACC_dK.  There is no room for a second S or G buffer, so the registers of the exp groups are the second buffer:
+// an exp thread pulls its 32 columns of S into registers as soon as S is complete and says so, which frees
+// region B for the next tile's S while this tile's exponentials are still being formed; it pulls G likewise,
+// and when all threads hold their G values (one named barrier) W and P are packed over region A.  ONE warp
+// issues every tensor-core product in the order  G(q), S(q+1), W(q) K_j, P(q) dV_j, G(q+1), ...  - the tensor
+// pipe executes one thread's products in order, so G(q+1) may be queued right behind the products that still
+// read W(q) and P(q), and S(q+1) covers the time the exp groups need between G(q) and W(q).
 //
 // Shared memory: K_i (then P_l for the Q product), V'_i (then X_i, once the last G product is done), the
 // right-hand side / staging tile, and two rings of two whole tiles (K_j; dV_j), each tile as two 64-column
@@ -28,7 +29,8 @@
 // Warp roles (640 threads): warp 0 K producer (tickets, K_i, V'_i, K_j, X_i), warp 2 dV producer (right-hand
 // side, flag waits, dV_j), warp 1 issues all products (warp 3 only fills the warpgroup), warps 4-19
 // are four exp groups of 128 threads (one row each; group g forms k-steps g and 4+g of every tile and owns output
-// columns 32g..32g+31).  Row-blocks are taken by ticket in dependency order; every wait is bounded.
+// columns 32g..32g+31).  K_j's last reader (W K_j) is issued before dV_j's (P dV_j), because K_j is the operand the
+// next but one tile wants first (for its S).  Row-blocks are taken by ticket in dependency order; every wait is bounded.
 #include <type_traits>
 #include "kernels.h"
 
@@ -43,7 +45,7 @@ struct RevDkSmem {
   alignas(8) uint64_t kt_full[2];
   uint64_t kt_empty[2], vt_full[2], vt_empty[2];
   uint64_t ki_full, ki_free, vpi_full, x_full, vx_free, g_done, vi_full, r_free, stage_full;
-  uint64_t s_full, g_full, pw_full[2];
+  uint64_t s_full, s_loaded, g_full, pw_full[2];
   uint64_t acc_full, acc_free, acck_full, acck_free, rhs_full, out_full, pq_full, q_full, p_full;
   uint64_t tk_full[2], tk_empty[2];
   int tk_slot[2];
@@ -53,13 +55,14 @@ struct RevDkSmem {
 
 enum RevDkBar : int {
   RD_KT_FULL = 301, RD_KT_EMPTY, RD_VT_FULL, RD_VT_EMPTY, RD_KI_FULL, RD_KI_FREE, RD_VPI_FULL, RD_X_FULL, RD_VX_FREE,
-  RD_G_DONE, RD_VI_FULL, RD_R_FREE, RD_STAGE_FULL, RD_S_FULL, RD_G_FULL, RD_PW_FULL, RD_ACC_FULL, RD_ACC_FREE,
+  RD_G_DONE, RD_VI_FULL, RD_R_FREE, RD_STAGE_FULL, RD_S_FULL, RD_S_LOADED, RD_G_FULL, RD_PW_FULL, RD_ACC_FULL, RD_ACC_FREE,
   RD_ACCK_FULL, RD_ACCK_FREE, RD_RHS_FULL, RD_OUT_FULL, RD_PQ_FULL, RD_Q_FULL, RD_P_FULL, RD_TK_FULL, RD_TK_EMPTY
 };
 
 constexpr int kRdThreads = 640;
 constexpr int kRdExp = 512;
-constexpr int kRdS = 0, kRdG = 128, kRdAcc = 256, kRdAccK = 384;
+constexpr int kRdS = 0, kRdG = 128, kRdAcc = 256, kRdAccK = 384;   // region B (S, Q), region A (G, then W and P)
+constexpr int kRdP = kRdG, kRdW = kRdG + 64;        // packed operands of a tile: k-step ks at +8 ks
 constexpr int kRdRegsService = 64, kRdRegsExp = 104;
 
 template <bool kBf16>
@@ -99,6 +102,7 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
     mbar_init(&s.r_free, 1);
     mbar_init(&s.stage_full, kRdExp);
     mbar_init(&s.s_full, 1);
+    mbar_init(&s.s_loaded, kRdExp);
     mbar_init(&s.g_full, 1);
     mbar_init(&s.acc_full, 1);
     mbar_init(&s.acc_free, kRdExp);
@@ -268,9 +272,10 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           ++ng;
         }
         tc_fence_after_sync();
-        for (int q = 0; q < n; ++q, ++g) {
-          const uint32_t st = g & 1;
-          if (!wait_barrier(&s.kt_full[st], (g >> 1) & 1, cta_abort, ctl, limit, chain, i, RD_KT_FULL)) { alive = false; break; }
+        // S of a tile into region B (the exp groups hold the S of the tile before in registers)
+        auto issue_s = [&](uint32_t gt) -> bool {
+          const uint32_t st = gt & 1;
+          if (!wait_barrier(&s.kt_full[st], (gt >> 1) & 1, cta_abort, ctl, limit, chain, i, RD_KT_FULL)) return false;
           tc_fence_after_sync();
           const uint64_t dbk = d_kr0 + st * (kTileBytes >> 4);
 #pragma unroll
@@ -279,11 +284,15 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
             umma_ss_w(tmem + kRdS, d_ki + off, dbk + off, idesc_kk, k ? 1u : 0u);
           }
           umma_commit_w(&s.s_full);
-          if (q == n - 1) {
-            // the newest predecessor: S only; K_j has no other reader, dV_j is read by the closing product below
-            umma_commit_w(&s.kt_empty[st]);
-            break;
-          }
+          return true;
+        };
+        if (n >= 1) {
+          if (!issue_s(g)) break;
+          if (n == 1) umma_commit_w(&s.kt_empty[g & 1]);     // the newest predecessor's K_j has no other reader
+        }
+        for (int q = 0; q + 1 < n; ++q, ++g) {
+          const uint32_t st = g & 1;
+          // ---- G(q) into region A (its previous readers, the products of the tile before, were issued above) ----
           if (!wait_barrier(&s.vt_full[st], (g >> 1) & 1, cta_abort, ctl, limit, chain, i, RD_VT_FULL)) { alive = false; break; }
           tc_fence_after_sync();
           const uint64_t dbv = d_vr0 + st * (kTileBytes >> 4);
@@ -294,32 +303,34 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           }
           umma_commit_w(&s.g_full);
           if (q == n - 2) umma_commit_w(&s.g_done);      // V'_i is no longer needed: X_i may take its buffer
-          // ---- ACC_dV += P dV_j, ACC_dK += W K_j, four k-steps per round ----
+          // ---- S(q+1): region B is free once every exp thread has S(q) in registers ----
+          if (!wait_barrier(&s.s_loaded, gf & 1, cta_abort, ctl, limit, chain, i, RD_S_LOADED)) { alive = false; break; }
+          if (!issue_s(g + 1)) { alive = false; break; }
+          if (q + 1 == n - 1) umma_commit_w(&s.kt_empty[(g + 1) & 1]);   // S_l was K_l's only reader
+          // ---- ACC_dK += W K_j, then ACC_dV += P dV_j ----
           const uint64_t dbv_mn = d_vr0_mn + st * (kTileBytes >> 4);
           const uint64_t dbk_mn = d_kr0_mn + st * (kTileBytes >> 4);
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            if (!wait_barrier(&s.pw_full[c], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
-            if (q == 0 && c == 0) {
-              // the accumulators of the item before have been read out
-              if (!wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, RD_ACC_FREE) ||
-                  !wait_barrier(&s.acck_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, RD_ACCK_FREE)) {
-                alive = false;
-                break;
-              }
-            }
-            tc_fence_after_sync();
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const int ks = 4 * c + kk;       // k-step: rows 16 ks .. of the tile; its packed operand sits at column 16 ks
-              umma_ts_w(tmem + kRdAcc, tmem + kRdS + 16 * ks, dbv_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
-              umma_ts_w(tmem + kRdAccK, tmem + kRdG + 16 * ks, dbk_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
+          if (q == 0) {
+            // the accumulators of the item before have been read out
+            if (!wait_barrier(&s.acc_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, RD_ACC_FREE) ||
+                !wait_barrier(&s.acck_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, RD_ACCK_FREE)) {
+              alive = false;
+              break;
             }
           }
-          if (!alive) break;
-          ++gf;
+          if (!wait_barrier(&s.pw_full[0], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts_w(tmem + kRdAccK, tmem + kRdW + 8 * ks, dbk_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.kt_empty[st]);
+          if (!wait_barrier(&s.pw_full[1], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts_w(tmem + kRdAcc, tmem + kRdP + 8 * ks, dbv_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.vt_empty[st]);
+          ++gf;
         }
         if (!alive) break;
         if (n < 2) {
@@ -394,44 +405,48 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
       const int b = chain / H, h = chain % H;
       const float lam = args.lam_inv[(chain * T + i) * kBlock + row];
 
-      // ---- full tiles: P = exp(S), W = -P o G, k-steps wg (round 0) and 4 + wg (round 1) ----
-      // The exponentials of round 0 are formed while the G product is still running.
+      // ---- full tiles: P = exp(S), W = -P o G for k-steps wg and 4 + wg (columns 16 wg .. and 64 + 16 wg ..) ----
       for (int q = 0; q + 1 < n; ++q, ++g, ++gf) {
         if (!wait_barrier(&s.s_full, g & 1, cta_abort, ctl, limit, chain, i, RD_S_FULL)) { alive = false; break; }
         tc_fence_after_sync();
-        uint32_t sv0[16], sv1[16], gv[16];
-        tmem_ld16(lane_base + kRdS + 16 * wg, sv0);
-        tmem_ld16(lane_base + kRdS + 64 + 16 * wg, sv1);
+        uint32_t sv[32], gv[32];
+        tmem_ld16(lane_base + kRdS + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&sv[0]));
+        tmem_ld16(lane_base + kRdS + 64 + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&sv[16]));
         tmem_wait_ld();
-        float ev[16];
+        tc_fence_before_sync();
+        mbar_arrive(&s.s_loaded);            // region B may take the next tile's S
+        float ev[32];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) ev[e] = ex2_approx(__uint_as_float(sv0[e]) * xs);
+        for (int e = 0; e < 32; ++e) ev[e] = ex2_approx(__uint_as_float(sv[e]) * xs);
         if (!wait_barrier(&s.g_full, gf & 1, cta_abort, ctl, limit, chain, i, RD_G_FULL)) { alive = false; break; }
         tc_fence_after_sync();
-        tmem_ld16(lane_base + kRdG + 16 * wg, gv);
+        tmem_ld16(lane_base + kRdG + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&gv[0]));
+        tmem_ld16(lane_base + kRdG + 64 + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&gv[16]));
         tmem_wait_ld();
+        // W and P are packed over G's columns, other threads' included: everybody holds its G values first
+        named_bar_sync(2, kRdExp);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const uint32_t col = 16 * (4 * c + wg);
-          uint32_t pk[8], wk[8];
+          uint32_t wk[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            pk[e] = pack2_fast<kBf16>(ev[2 * e], ev[2 * e + 1]);
-            wk[e] = pack2_fast<kBf16>(-ev[2 * e] * __uint_as_float(gv[2 * e]), -ev[2 * e + 1] * __uint_as_float(gv[2 * e + 1]));
-          }
-          tmem_st8(lane_base + kRdS + col, pk);
-          tmem_st8(lane_base + kRdG + col, wk);
-          if (c == 0) {
-            // round 1's operands come in while round 0's stores drain
-            tmem_ld16(lane_base + kRdG + 64 + 16 * wg, gv);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) ev[e] = ex2_approx(__uint_as_float(sv1[e]) * xs);
-            tmem_wait_ld();
-          }
-          tmem_wait_st();
-          tc_fence_before_sync();
-          mbar_arrive(&s.pw_full[c]);
+          for (int e = 0; e < 8; ++e)
+            wk[e] = pack2_fast<kBf16>(-ev[16 * c + 2 * e] * __uint_as_float(gv[16 * c + 2 * e]),
+                                      -ev[16 * c + 2 * e + 1] * __uint_as_float(gv[16 * c + 2 * e + 1]));
+          tmem_st8(lane_base + kRdW + 8 * (4 * c + wg), wk);
         }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&s.pw_full[0]);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pk[e] = pack2_fast<kBf16>(ev[16 * c + 2 * e], ev[16 * c + 2 * e + 1]);
+          tmem_st8(lane_base + kRdP + 8 * (4 * c + wg), pk);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&s.pw_full[1]);
       }
       if (!alive) break;
 
