@@ -127,6 +127,20 @@ __device__ __forceinline__ bool wait_flag(const int* flag, volatile int* cta_abo
   return ok;
 }
 
+// Tiles of an item are visited oldest predecessor first, the newest (tile n - 1) last.  A row-block raises its
+// flag only after it has acquired the flags of all its predecessors, so a flag that is up vouches (with its
+// acquire) for every block published before it.  Looks once at the flag of tile n - kFlagProbe (row-block
+// `probe_row` of the chain whose flags start at `chain_flags`) and returns the number of leading tiles that need
+// no flag check of their own: n - kFlagProbe + 1 if that flag is up, else 0.  The proxy fence that must stand
+// between an acquire in the generic proxy and TMA loads of the data is issued here when the answer is not 0.
+constexpr int kFlagProbe = 48;
+__device__ __forceinline__ int flags_known_up(const int* chain_flags, int n, int probe_row) {
+  if (n <= kFlagProbe) return 0;
+  if (ld_acquire_gpu(chain_flags + probe_row) < kFlagComplete) return 0;
+  fence_proxy_async_all();
+  return n - kFlagProbe + 1;
+}
+
 // Event trace of one CTA (debugging builds only): role r appends {tag, q, clock} triples.
 #ifdef LUCID_TRACE
 constexpr int kTraceMax = 8192;

@@ -211,6 +211,11 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           tma_load_4d(s.rhs + kHalfBytes, &tm_dvp, &s.vi_full, 64, i * kBlock, h, b);
           vi_loaded = true;
         };
+        // A row-block publishes itself only after it has acquired the flags of all its predecessors, so one
+        // flag that is up vouches for every block published before it: one look at the block kFlagProbe steps
+        // behind the newest predecessor usually spares the older tiles their flag round trip (an L2 round trip
+        // in series with every tile load otherwise).
+        const int skip_until = flags_known_up(args.flags + chain * T, n, T - 1 - (n - kFlagProbe));
         for (int q = 0; q < n; ++q, ++g) {
           const int j = T - 1 - q;
           if (!vi_loaded && mbar_try_wait(&s.r_free, (it & 1) ^ 1)) load_vi();
@@ -219,11 +224,13 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
             alive = false;
             break;
           }
-          if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j, nullptr)) {
-            alive = false;
-            break;
+          if (q >= skip_until) {
+            if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j, nullptr)) {
+              alive = false;
+              break;
+            }
+            fence_proxy_async_all();   // flag acquired in the generic proxy; the tile is read by TMA
           }
-          fence_proxy_async_all();   // flag acquired in the generic proxy; the tile is read by TMA
           mbar_expect_tx(&s.vt_full[st], kTileBytes);
           tma_load_4d(s.vring[st], &tm_dv, &s.vt_full[st], 0, j * kBlock, h, b);
           tma_load_4d(s.vring[st] + kHalfBytes, &tm_dv, &s.vt_full[st], 64, j * kBlock, h, b);

@@ -320,6 +320,9 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           vi_loaded = true;
         };
         unsigned long long waited = 0;
+        // one look at the block kFlagProbe steps behind the newest predecessor usually spares the older tiles
+        // their own flag round trip (see flags_known_up)
+        const int skip_until = P.no_sync ? 0 : flags_known_up(args.flags + chain * T, n, tile_j(jfirst, n - kFlagProbe));
         for (int q = 0; q < n && alive; ++q) {
           const int j = tile_j(jfirst, q);
           if (!vi_loaded && mbar_try_wait(&s.r_free, (it & 1) ^ 1)) load_vi();
@@ -340,7 +343,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
             u += 2;
             continue;
           }
-          if (!P.no_sync) {
+          if (!P.no_sync && q >= skip_until) {
             if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j,
                            P.instrument ? &waited : nullptr)) {
               alive = false;

@@ -188,7 +188,8 @@ def test_backward_in_one_launch_matches_separate_launches(ops, dtype, H):
     Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
     vp = ops._forward_sub_fwd(Kc, Vc, check=True)
     try:
-        lib.lucid_set_fused_backward(0, 0)                      # separate launches
+        lib.lucid_set_fused_backward(0, 0)                      # separate launches: reverse solve, then dK over all tiles
+        lib.lucid_set_upper_in_solve(0)
         dv0, dk0 = ops._forward_sub_bwd(Kc, vp, Gc, use_combined_kernel=True, check=True)
         for solve_ctas in (0, 20, 120):                         # automatic share, a small and a large one
             lib.lucid_set_fused_backward(2, solve_ctas)
@@ -203,6 +204,7 @@ def test_backward_in_one_launch_matches_separate_launches(ops, dtype, H):
     finally:
         lib.lucid_set_fused_backward(2, 0)                      # library defaults
         lib.lucid_set_dk_split(1)
+        lib.lucid_set_upper_in_solve(1)
     assert bool(torch.isfinite(dk0.float()).all())
 
 
