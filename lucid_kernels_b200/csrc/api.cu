@@ -223,6 +223,7 @@ static int run_solve(bool reverse, const void* k, const void* in, void* out, con
     ra.flags = sa.flags;
     ra.ctl = sa.ctl;
     ra.upper = upper->upper;
+    ra.trace = g_trace;
     ra.p = p;
     e = launch_revdk(bf16, tm_k, tm_in, tm_st, upper->tm_vp, tm_x, ra, grid, stream);
   } else if (fused) {

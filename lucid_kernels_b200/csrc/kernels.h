@@ -46,6 +46,7 @@ struct RevDkArgs {
   int* flags;               // (C, T)
   Control* ctl;
   float* upper;             // (C*T, 128, 128) fp32: sum over j >= i + 2 of W_ij K_j, unscaled
+  long long* trace;         // debugging builds only (LUCID_TRACE); null otherwise
   Problem p;
 };
 

@@ -145,6 +145,8 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
       tma_prefetch_desc(&tm_x);
       uint32_t g = 0, ng = 0;      // tiles loaded; items that had G products (phase of g_done)
       bool alive = true;
+      int trc = 0;
+      (void)trc;
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_empty[slot], ((it >> 1) & 1) ^ 1, cta_abort, ctl, limit, -1, -1, RD_TK_EMPTY)) break;
@@ -173,6 +175,7 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
             alive = false;
             break;
           }
+          LUCID_TR(args.trace, 0, trc, 41, g);
           mbar_expect_tx(&s.kt_full[st], kTileBytes);
           tma_load_4d(s.kring[st], &tm_k, &s.kt_full[st], 0, j * kBlock, h, b);
           tma_load_4d(s.kring[st] + kHalfBytes, &tm_k, &s.kt_full[st], 64, j * kBlock, h, b);
@@ -196,6 +199,8 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
       tma_prefetch_desc(&tm_dv);
       uint32_t g = 0;
       bool alive = true;
+      int trc = 0;
+      (void)trc;
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, RD_TK_FULL)) break;
@@ -224,6 +229,7 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
             alive = false;
             break;
           }
+          LUCID_TR(args.trace, 1, trc, 30, g);
           if (q >= skip_until) {
             if (!wait_flag(args.flags + chain * T + j, cta_abort, ctl, limit, chain, i, j, nullptr)) {
               alive = false;
@@ -231,6 +237,7 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
             }
             fence_proxy_async_all();   // flag acquired in the generic proxy; the tile is read by TMA
           }
+          LUCID_TR(args.trace, 1, trc, 32, g);
           mbar_expect_tx(&s.vt_full[st], kTileBytes);
           tma_load_4d(s.vring[st], &tm_dv, &s.vt_full[st], 0, j * kBlock, h, b);
           tma_load_4d(s.vring[st] + kHalfBytes, &tm_dv, &s.vt_full[st], 64, j * kBlock, h, b);
@@ -264,6 +271,10 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
       const uint64_t d_vr0_mn = umma_smem_desc(smem_u32(s.vring[0]), kHalfBytes, 1024);
       uint32_t g = 0, gf = 0, ng = 0, nq = 0;
       bool alive = true;
+      int trc = 0;
+      (void)trc;
+      const bool leader = lane == 0;
+      (void)leader;
       for (int it = 0; alive; ++it) {
         const int slot = it & 1;
         if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, RD_TK_FULL)) break;
@@ -284,13 +295,18 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           const uint32_t st = gt & 1;
           if (!wait_barrier(&s.kt_full[st], (gt >> 1) & 1, cta_abort, ctl, limit, chain, i, RD_KT_FULL)) return false;
           tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 2, trc, 18, gt);
           const uint64_t dbk = d_kr0 + st * (kTileBytes >> 4);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
             umma_ss_w(tmem + kRdS, d_ki + off, dbk + off, idesc_kk, k ? 1u : 0u);
+#ifdef LUCID_TRACE_MMA
+            if (leader) LUCID_TR(args.trace, 2, trc, 50 + k, gt);
+#endif
           }
           umma_commit_w(&s.s_full);
+          if (leader) LUCID_TR(args.trace, 2, trc, 12, gt);
           return true;
         };
         if (n >= 1) {
@@ -300,18 +316,25 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
         for (int q = 0; q + 1 < n; ++q, ++g) {
           const uint32_t st = g & 1;
           // ---- G(q) into region A (its previous readers, the products of the tile before, were issued above) ----
+          if (leader) LUCID_TR(args.trace, 2, trc, 9, g);
           if (!wait_barrier(&s.vt_full[st], (g >> 1) & 1, cta_abort, ctl, limit, chain, i, RD_VT_FULL)) { alive = false; break; }
           tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 2, trc, 17, g);
           const uint64_t dbv = d_vr0 + st * (kTileBytes >> 4);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
             umma_ss_w(tmem + kRdG, d_vpi + off, dbv + off, idesc_kk, k ? 1u : 0u);
+#ifdef LUCID_TRACE_MMA
+            if (leader) LUCID_TR(args.trace, 2, trc, 60 + k, g);
+#endif
           }
           umma_commit_w(&s.g_full);
+          if (leader) LUCID_TR(args.trace, 2, trc, 10, g);
           if (q == n - 2) umma_commit_w(&s.g_done);      // V'_i is no longer needed: X_i may take its buffer
           // ---- S(q+1): region B is free once every exp thread has S(q) in registers ----
           if (!wait_barrier(&s.s_loaded, gf & 1, cta_abort, ctl, limit, chain, i, RD_S_LOADED)) { alive = false; break; }
+          if (leader) LUCID_TR(args.trace, 2, trc, 11, g);
           if (!issue_s(g + 1)) { alive = false; break; }
           if (q + 1 == n - 1) umma_commit_w(&s.kt_empty[(g + 1) & 1]);   // S_l was K_l's only reader
           // ---- ACC_dK += W K_j, then ACC_dV += P dV_j ----
@@ -327,16 +350,20 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           }
           if (!wait_barrier(&s.pw_full[0], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
           tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 2, trc, 13, g);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             umma_ts_w(tmem + kRdAccK, tmem + kRdW + 8 * ks, dbk_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.kt_empty[st]);
+          if (leader) LUCID_TR(args.trace, 2, trc, 14, g);
           if (!wait_barrier(&s.pw_full[1], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
           tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 2, trc, 15, g);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             umma_ts_w(tmem + kRdAcc, tmem + kRdP + 8 * ks, dbv_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.vt_empty[st]);
+          if (leader) LUCID_TR(args.trace, 2, trc, 16, g);
           ++gf;
         }
         if (!alive) break;
@@ -400,6 +427,10 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
     const uint32_t vec0 = (wg & 1) * 4;
     uint32_t g = 0, gf = 0, nq = 0;
     bool alive = true;
+    int trc = 0;
+    (void)trc;
+    const bool tr_lead = tid == 128;
+    (void)tr_lead;
     typedef typename std::conditional<kBf16, __nv_bfloat16, __half>::type elem_t;
     for (int it = 0; alive; ++it) {
       const int slot = it & 1;
@@ -414,24 +445,31 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
 
       // ---- full tiles: P = exp(S), W = -P o G for k-steps wg and 4 + wg (columns 16 wg .. and 64 + 16 wg ..) ----
       for (int q = 0; q + 1 < n; ++q, ++g, ++gf) {
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 19, g);
         if (!wait_barrier(&s.s_full, g & 1, cta_abort, ctl, limit, chain, i, RD_S_FULL)) { alive = false; break; }
         tc_fence_after_sync();
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 20, g);
         uint32_t sv[32], gv[32];
         tmem_ld16(lane_base + kRdS + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&sv[0]));
         tmem_ld16(lane_base + kRdS + 64 + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&sv[16]));
         tmem_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(&s.s_loaded);            // region B may take the next tile's S
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 21, g);
         float ev[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) ev[e] = ex2_approx(__uint_as_float(sv[e]) * xs);
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 22, g);
         if (!wait_barrier(&s.g_full, gf & 1, cta_abort, ctl, limit, chain, i, RD_G_FULL)) { alive = false; break; }
         tc_fence_after_sync();
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 23, g);
         tmem_ld16(lane_base + kRdG + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&gv[0]));
         tmem_ld16(lane_base + kRdG + 64 + 16 * wg, *reinterpret_cast<uint32_t(*)[16]>(&gv[16]));
         tmem_wait_ld();
         // W and P are packed over G's columns, other threads' included: everybody holds its G values first
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 24, g);
         named_bar_sync(2, kRdExp);
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 25, g);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t wk[8];
@@ -444,6 +482,7 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&s.pw_full[0]);
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 26, g);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[8];
@@ -454,6 +493,7 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&s.pw_full[1]);
+        if (tr_lead) LUCID_TR(args.trace, 3, trc, 27, g);
       }
       if (!alive) break;
 
