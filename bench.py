@@ -460,6 +460,13 @@ def main():
         clocks["sm_mhz_in_kernel_error"] = str(exc)[:80]
         wavefront = None
 
+    # ---- the operand-delivery ceiling as measured: TMA boxes of this run's K from L2 into every SM at once ----
+    try:
+        # on as many systems as one scheduler group of the solve holds (four at N = 32768: an L2-resident stream)
+        delivery = _cabi.tma_delivery_rate(sets[0][0][:1, :, :4], slots=4, boxes_per_sm=4000)
+    except Exception as exc:      # reporting only; never fails the benchmark
+        delivery = dict(error=str(exc)[:80])
+
     def check_status():
         for ent in list(_cabi._workspaces.values()):      # the eager calls' workspace and the graphs' ones
             st = _cabi.read_status(ent.buf, torch.cuda.current_stream().cuda_stream)
@@ -698,6 +705,17 @@ def main():
         for v in kern.values():
             v["tflops"] = v["algo"] / (v["ms"] * 1e-3) / 1e12
             v["executed_tflops"] = v["executed"] / (v["ms"] * 1e-3) / 1e12
+        # Operand bytes the kernels stream from L2 into shared memory: two 32 KiB tiles per tile of work (K_j and
+        # Y_j / dV_j / V'_j) and three per row-block (its own K_i, X_i or A_i and right-hand side); the dK kernel
+        # in its lower-part mode visits the lower tiles, the diagonal tile twice and one upper tile per row-block.
+        tile_b = 32768.0
+        for name, v in kern.items():
+            tiles = pairs_local + (2 * diag_local if name.startswith("dk_kernel (lower") else
+                                   pairs_local + diag_local if name.startswith("dk_kernel") else 0)
+            v["operand_bytes"] = (2 * tiles + 3 * diag_local) * tile_b * (2 if name.startswith("bwd_fused") else 1)
+            v["operand_tb_per_s"] = v["operand_bytes"] / (v["ms"] * 1e-3) / 1e12
+            if delivery and "tb_per_s" in delivery:
+                v["frac_of_delivery"] = v["operand_tb_per_s"] / delivery["tb_per_s"]
         dom_kernel = max(kern, key=lambda name: kern[name]["ms"])
         dom_tflops = kern[dom_kernel]["tflops"]
         # DRAM bytes per launch of the dominant kernel: its compulsory bytes (every ncu capture of these kernels
@@ -713,8 +731,12 @@ def main():
                         frac_sustained=dom_tflops / peaks["bf16_tflops_sustained"], traffic=traffic,
                         peak_source=peaks["source"] + (" (sustained: kernels ran at its clock)" if at_sustained else " (burst)"),
                         per_kernel_ms=k_ms, executed_tflops=kern[dom_kernel]["executed_tflops"],
-                        per_kernel={name: dict(ms=v["ms"], tflops=v["tflops"], executed_tflops=v["executed_tflops"])
-                                    for name, v in kern.items()})
+                        per_kernel={name: {k: v[k] for k in ("ms", "tflops", "executed_tflops", "operand_tb_per_s",
+                                                             "frac_of_delivery") if k in v}
+                                    for name, v in kern.items()},
+                        delivery=dict(delivery or {}, what="TMA delivery of 16 KiB operand boxes from L2 into all SMs "
+                                                           "at once, measured in this run (lucid_probe_tma_delivery): "
+                                                           "the ceiling of per_kernel.operand_tb_per_s"))
         # Bounds asked for by the metric: the tensor roofline of the algorithmic flops on this many GPUs and
         # the critical path of the two solves - T - 1 hand-overs each at the median chain step measured in THIS
         # run by the instrumented forward (in pair mode the two kinds of hand-over separately); the fraction

@@ -132,6 +132,16 @@ int lucid_bwd_sub(const void* k, const void* v_prime, const void* dv_prime, void
  * (forward_sub_fwd.py:536-544). */
 int lucid_read_status(const void* workspace, void* cuda_stream, int32_t out[8]);
 
+/* Diagnostic, no counterpart in the reference: measures how fast TMA delivers operand tiles from L2 into the
+ * shared memory of every SM at once - the ceiling of the solve and dK kernels' operand streams (64 KiB per
+ * tile of work each), whatever they compute.  One CTA per SM (at most clocks_len of them) streams
+ * boxes_per_sm 16 KiB boxes (64 columns x 128 rows) of the (B, N, H, 128) 16-bit tensor - the loads the kernels
+ * issue - through a ring of `slots` stages (1..12) and writes to clocks[cta] (device memory) the SM clocks that
+ * took, or -1 if a wait ran out.  Bytes per clock per SM = boxes_per_sm * 16384 / clocks[cta].  Asynchronous
+ * on cuda_stream; returns 0, a negative LUCID_E_* code or a cudaError_t. */
+int lucid_probe_tma_delivery(const void* tensor, const int64_t strides[3], int B, int N, int H, int dtype, int slots,
+                             int boxes_per_sm, long long* clocks, int clocks_len, void* cuda_stream);
+
 /* Human-readable name of a status word out[0] or of a negative return code. */
 const char* lucid_status_string(int code);
 

@@ -30,7 +30,8 @@ EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_rea
            "lucid_status_string", "lucid_set_wait_limit_ns", "lucid_workspace_timestamps_offset",
            "lucid_profile_next_call", "lucid_set_head_steps", "lucid_set_group_overlap", "lucid_set_dk_split", "lucid_fwd_sub_static",
            "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled",
-           "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve", "lucid_set_solve_variant", "lucid_set_upper_in_solve", "lucid_query_upper_in_solve")
+           "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve", "lucid_set_solve_variant", "lucid_set_upper_in_solve", "lucid_query_upper_in_solve",
+           "lucid_probe_tma_delivery")
 
 
 class LucidKernelError(RuntimeError):
@@ -100,6 +101,9 @@ def load() -> ctypes.CDLL:
                                              c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
                                              c.c_int, c.c_float, c.c_void_p, c.c_size_t, c.c_void_p]
         lib.lucid_read_status.restype = c.c_int
+        lib.lucid_probe_tma_delivery.restype = c.c_int
+        lib.lucid_probe_tma_delivery.argtypes = [c.c_void_p, _I64x3, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
+                                                 c.c_int, c.c_void_p, c.c_int, c.c_void_p]
         lib.lucid_read_status.argtypes = [c.c_void_p, c.c_void_p, c.POINTER(c.c_int32)]
         lib.lucid_status_string.restype = c.c_char_p
         lib.lucid_status_string.argtypes = [c.c_int]
@@ -234,3 +238,34 @@ def raise_on_device_error(ws: torch.Tensor, stream_ptr: int, what: str) -> None:
         kern = {0: "diag-prep", 1: "solve", 2: "dK"}.get(st[1], "?")
         raise LucidKernelError(
             f"{what}: {msg} [kernel={kern} chain={st[2]} row_block={st[3]} detail={st[4]} barrier={st[5]}]")
+
+
+def tma_delivery_rate(t: torch.Tensor, slots: int = 4, boxes_per_sm: int = 4000) -> dict:
+    """Measure how fast TMA delivers 16 KiB operand boxes of the (B, N, H, 128) tensor ``t`` from L2 into the
+    shared memory of all SMs at once (``lucid_probe_tma_delivery``): the ceiling of the operand streams of the
+    solve and dK kernels.  Returns bytes per clock per SM (mean over the SMs, from the SM clock counters) and
+    the whole-GPU rate in TB/s (from CUDA events around a second launch; the first warms the caches)."""
+    assert t.is_cuda and t.dim() == 4 and t.shape[3] == 128
+    B, N, H, _ = t.shape
+    lib = load()
+    sms = torch.cuda.get_device_properties(t.device).multi_processor_count
+    clocks = torch.zeros(sms, dtype=torch.int64, device=t.device)
+    stream = torch.cuda.current_stream(t.device)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for timed in (False, True):
+        if timed:
+            ev0.record(stream)
+        rc = lib.lucid_probe_tma_delivery(t.data_ptr(), strides3(t), B, N, H, dtype_code(t.dtype), slots,
+                                          boxes_per_sm, clocks.data_ptr(), sms, stream.cuda_stream)
+        check_rc(rc, "lucid_probe_tma_delivery")
+        if timed:
+            ev1.record(stream)
+    stream.synchronize()
+    c = clocks.cpu()
+    if int(c.min()) <= 0:
+        raise LucidKernelError("lucid_probe_tma_delivery: a wait ran out")
+    ms = ev0.elapsed_time(ev1)
+    total = float(sms) * boxes_per_sm * 16384
+    return {"bytes_per_clk_per_sm": boxes_per_sm * 16384 / float(c.double().mean()),
+            "tb_per_s": total / (ms * 1e-3) / 1e12, "ms": ms, "sms": sms, "slots": slots,
+            "boxes_per_sm": boxes_per_sm}

@@ -16,7 +16,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "_lucid_b200.so")
-SOURCES = ["api.cu", "solve.cu", "diag_prep.cu", "dk.cu", "bwd_fused.cu", "rev_dk.cu"]
+SOURCES = ["api.cu", "solve.cu", "diag_prep.cu", "dk.cu", "bwd_fused.cu", "rev_dk.cu", "probe.cu"]
 # sources that textually include other sources
 INCLUDES = {"bwd_fused.cu": ["solve.cu", "dk.cu"]}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

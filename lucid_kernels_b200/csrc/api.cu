@@ -505,6 +505,23 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
   return 0;
 }
 
+int lucid_probe_tma_delivery(const void* tensor, const int64_t strides[3], int B, int N, int H, int dtype, int slots,
+                             int boxes_per_sm, long long* clocks, int clocks_len, void* cuda_stream) {
+  int rc = check_shape(B, N, H, kBlock, dtype);
+  if (rc) return rc;
+  if ((rc = check_tensor(tensor, strides, B, N, H))) return rc;
+  if (!clocks) return LUCID_E_NULL_POINTER;
+  if (slots < 1 || slots > 12 || boxes_per_sm < 1 || clocks_len < 1) return LUCID_E_BAD_SHAPE;
+  const int sms = sm_count();
+  if (sms <= 0) return LUCID_E_NO_DEVICE;
+  CUtensorMap tm;
+  if ((rc = bshd_map(&tm, dtype == LUCID_DTYPE_BF16, tensor, strides, B, N, H, 128))) return rc;
+  const int grid = sms < clocks_len ? sms : clocks_len;
+  cudaError_t e = launch_delivery_probe(tm, slots, boxes_per_sm, B * H, N / kBlock, H, clocks, grid,
+                                        static_cast<cudaStream_t>(cuda_stream));
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
 int lucid_read_status(const void* workspace, void* cuda_stream, int32_t out[8]) {
   if (!workspace || !out) return LUCID_E_NULL_POINTER;
   int32_t host[24];

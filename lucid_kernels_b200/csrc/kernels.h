@@ -72,4 +72,9 @@ cudaError_t launch_bwd_fused(bool bf16, const CUtensorMap& tm_k, const CUtensorM
                              const CUtensorMap& tm_dv, const SolveArgs& sargs, const DkArgs& dargs, int n_solve,
                              int* arrivals, int grid, cudaStream_t stream);
 
+// Diagnostic (probe.cu): `grid` CTAs each stream `boxes` 16 KiB boxes of the tensor behind tm (box 64 x 128)
+// through a ring of `slots` stages and write the SM clocks that took to clocks[cta] (-1: a wait ran out).
+cudaError_t launch_delivery_probe(const CUtensorMap& tm, int slots, int boxes, int chains, int T, int H,
+                                  long long* clocks, int grid, cudaStream_t stream);
+
 }  // namespace lucid

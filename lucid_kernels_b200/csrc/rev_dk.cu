@@ -48,6 +48,10 @@ struct RevDkSmem {
   uint64_t s_full, s_loaded, g_full, pw_full[2];
   uint64_t acc_full, acc_free, acck_full, acck_free, rhs_full, out_full, pq_full, q_full, p_full;
   uint64_t tk_full[2], tk_empty[2];
+#ifdef LUCID_TRACE
+  uint64_t tr_done[4];      // debugging builds: completion of the G, S, W K_j and P dV_j products of a tile
+  int tr_stop;
+#endif
   int tk_slot[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -114,6 +118,10 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
     mbar_init(&s.q_full, 1);
     mbar_init(&s.p_full, kRdExp);
     s.abort_flag = 0;
+#ifdef LUCID_TRACE
+    for (int i = 0; i < 4; ++i) mbar_init(&s.tr_done[i], 1);
+    s.tr_stop = 0;
+#endif
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -306,6 +314,9 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
 #endif
           }
           umma_commit_w(&s.s_full);
+#ifdef LUCID_TRACE
+          umma_commit_w(&s.tr_done[1]);
+#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 12, gt);
           return true;
         };
@@ -330,6 +341,9 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
 #endif
           }
           umma_commit_w(&s.g_full);
+#ifdef LUCID_TRACE
+          umma_commit_w(&s.tr_done[0]);
+#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 10, g);
           if (q == n - 2) umma_commit_w(&s.g_done);      // V'_i is no longer needed: X_i may take its buffer
           // ---- S(q+1): region B is free once every exp thread has S(q) in registers ----
@@ -355,6 +369,9 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           for (int ks = 0; ks < 8; ++ks)
             umma_ts_w(tmem + kRdAccK, tmem + kRdW + 8 * ks, dbk_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.kt_empty[st]);
+#ifdef LUCID_TRACE
+          umma_commit_w(&s.tr_done[2]);
+#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 14, g);
           if (!wait_barrier(&s.pw_full[1], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
           tc_fence_after_sync();
@@ -363,6 +380,9 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           for (int ks = 0; ks < 8; ++ks)
             umma_ts_w(tmem + kRdAcc, tmem + kRdP + 8 * ks, dbv_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.vt_empty[st]);
+#ifdef LUCID_TRACE
+          umma_commit_w(&s.tr_done[3]);
+#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 16, g);
           ++gf;
         }
@@ -413,9 +433,28 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
         }
         umma_commit_w(&s.out_full);
       }
+#ifdef LUCID_TRACE
+      s.tr_stop = 1;
+#endif
     }
   } else if (warp == 3) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRdRegsService));   // fills the service warpgroup
+#ifdef LUCID_TRACE
+    if (lane == 0 && args.trace != nullptr) {
+      // debugging builds: the clock at which each group of products completed on the tensor pipe (tags 70-73:
+      // G, S, W K_j, P dV_j; q = how many of that kind completed before)
+      int trc = 0;
+      uint32_t cnt[4] = {0, 0, 0, 0};
+      volatile int* stop = &s.tr_stop;
+      while (!*stop && !*cta_abort) {
+        for (int b = 0; b < 4; ++b)
+          if (mbar_try_wait(&s.tr_done[b], cnt[b] & 1)) {
+            LUCID_TR(args.trace, 7, trc, 70 + b, cnt[b]);
+            ++cnt[b];
+          }
+      }
+    }
+#endif
   } else if (warp >= 4) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRdRegsExp));
     // =========================== exp groups + epilogue ===========================

@@ -539,3 +539,16 @@ def test_config_fwd_b1_n131072_h8_against_the_oracle(ops):
     assert ts.shape == (8, 1024, 8) and bool((ts[:, :, 2] > ts[:, :, 0]).all())
     e = _oracle_one_system(K, V, V, vp, None, None, 6)
     assert e[0] < 0.01, e
+
+
+def test_tma_delivery_probe_reports_a_rate(ops):
+    """The diagnostic that measures the operand-delivery ceiling: every SM reports a positive clock count and the
+    rate lies in the range the SM's L2 port allows (a 64-byte port: between a few and 64 bytes per clock)."""
+    from lucid_kernels_b200 import _cabi
+    K = torch.randn(2, 8192, 8, 128, device="cuda").bfloat16()
+    for slots in (1, 4):
+        r = _cabi.tma_delivery_rate(K, slots=slots, boxes_per_sm=500)
+        assert 2.0 < r["bytes_per_clk_per_sm"] < 64.0, r
+        assert r["tb_per_s"] > 0.5, r
+    with pytest.raises(_cabi.LucidKernelError):
+        _cabi.tma_delivery_rate(K, slots=13)
