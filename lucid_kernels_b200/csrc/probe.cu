@@ -31,27 +31,37 @@ delivery_probe_kernel(const __grid_constant__ CUtensorMap tm,   // box 64 x 128
   // CTAs are dealt over the chains like the solve's row-blocks, so several SMs stream the same tiles
   const int chain = blockIdx.x % chains, b = chain / H, h = chain % H;
   const long long t0 = clock64();
+  // stage and phase are carried along (no division in the loops: one thread has to issue a box every ~350 clocks)
   if (threadIdx.x == 0) {
+    int st = 0, tile = (blockIdx.x * 3) % T;      // the two 64-column halves of a tile, then the next tile
+    uint32_t ph = 0;
     for (int u = 0; u < boxes; ++u) {
-      const int st = u % slots;
       uint32_t spins = 0;
-      while (!mbar_try_wait(&empty[st], ((u / slots) & 1) ^ 1))
+      while (!mbar_try_wait(&empty[st], ph ^ 1))
         if (++spins > kProbeSpinLimit) return;
-      const int tile = ((u >> 1) + blockIdx.x * 3) % T;
       mbar_expect_tx(&full[st], kHalfBytes);
       tma_load_4d(base + st * kHalfBytes, &tm, &full[st], 64 * (u & 1), tile * kBlock, h, b);
+      if ((u & 1) && ++tile == T) tile = 0;
+      if (++st == slots) {
+        st = 0;
+        ph ^= 1;
+      }
     }
   } else if (threadIdx.x == 32) {
     long long result = -1;
-    int u = 0;
+    int st = 0, u = 0;
+    uint32_t ph = 0;
     for (; u < boxes; ++u) {
-      const int st = u % slots;
       uint32_t spins = 0;
       bool ok = true;
-      while (!mbar_try_wait(&full[st], (u / slots) & 1))
+      while (!mbar_try_wait(&full[st], ph))
         if (++spins > kProbeSpinLimit) { ok = false; break; }
       if (!ok) break;
       mbar_arrive(&empty[st]);
+      if (++st == slots) {
+        st = 0;
+        ph ^= 1;
+      }
     }
     if (u == boxes) result = clock64() - t0;
     clocks[blockIdx.x] = result;
