@@ -17,17 +17,19 @@
 // ACC_dK.  There is no room for a second S or G buffer, so the registers of the exp groups are the second buffer:
 // an exp thread pulls its 32 columns of S into registers as soon as S is complete and says so, which frees
 // region B for the next tile's S while this tile's exponentials are still being formed; it pulls G likewise,
-// and when all threads hold their G values (one named barrier) W and P are packed over region A.  ONE warp
-// issues every tensor-core product in the order  G(q), S(q+1), W(q) K_j, P(q) dV_j, G(q+1), ...  - the tensor
-// pipe executes one thread's products in order, so G(q+1) may be queued right behind the products that still
-// read W(q) and P(q), and S(q+1) covers the time the exp groups need between G(q) and W(q).
+// and when all threads hold their G values (one named barrier) W and P are packed over region A.  One warp
+// issues the products on region A in the order  G(q), W(q) K_j, P(q) dV_j, G(q+1), ...  - the tensor pipe executes
+// one thread's products in order, so G(q+1) may be queued right behind the products that still read W(q) and
+// P(q) - and an item's first S; another warp issues S(q+1) as soon as region B is free, which covers the time the
+// exp groups need between G(q) and W(q).
 //
 // Shared memory: K_i (then P_l for the Q product), V'_i (then X_i, once the last G product is done), the
 // right-hand side / staging tile, and two rings of two whole tiles (K_j; dV_j), each tile as two 64-column
 // panels so that it serves as a K-major operand (S, G) and as an MN-major operand (P dV_j, W K_j).
 //
 // Warp roles (640 threads): warp 0 K producer (tickets, K_i, V'_i, K_j, X_i), warp 2 dV producer (right-hand
-// side, flag waits, dV_j), warp 1 issues all products (warp 3 only fills the warpgroup), warps 4-19
+// side, flag waits, dV_j), warp 1 issues G, an item's first S and everything that reads P, W, Q or X, warp 3 issues
+// the other S products, warps 4-19
 // are four exp groups of 128 threads (one row each; group g forms k-steps g and 4+g of every tile and owns output
 // columns 32g..32g+31).  K_j's last reader (W K_j) is issued before dV_j's (P dV_j), because K_j is the operand the
 // next but one tile wants first (for its S).  Row-blocks are taken by ticket in dependency order; every wait is bounded.
@@ -48,10 +50,6 @@ struct RevDkSmem {
   uint64_t s_full, s_loaded, g_full, pw_full[2];
   uint64_t acc_full, acc_free, acck_full, acck_free, rhs_full, out_full, pq_full, q_full, p_full;
   uint64_t tk_full[2], tk_empty[2];
-#ifdef LUCID_TRACE
-  uint64_t tr_done[4];      // debugging builds: completion of the G, S, W K_j and P dV_j products of a tile
-  int tr_stop;
-#endif
   int tk_slot[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -94,7 +92,7 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
       mbar_init(&s.vt_empty[i], 1);
       mbar_init(&s.pw_full[i], kRdExp);
       mbar_init(&s.tk_full[i], 1);
-      mbar_init(&s.tk_empty[i], 2 + 16);
+      mbar_init(&s.tk_empty[i], 3 + 16);
     }
     mbar_init(&s.ki_full, 1);
     mbar_init(&s.ki_free, 1);
@@ -118,10 +116,6 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
     mbar_init(&s.q_full, 1);
     mbar_init(&s.p_full, kRdExp);
     s.abort_flag = 0;
-#ifdef LUCID_TRACE
-    for (int i = 0; i < 4; ++i) mbar_init(&s.tr_done[i], 1);
-    s.tr_stop = 0;
-#endif
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -259,10 +253,10 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
     }
   } else if (warp == 1) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRdRegsService));
-    // =========================== the issuer of every product ===========================
-    // Program order per tile: S, G, then (as the exp groups deliver them) the products that read P and W; the
-    // next tile's S and G follow at once.  The tensor pipe runs one thread's products in order, so the S and G
-    // columns are never overwritten before the products that read them have done so.
+    // =========================== the issuer of all products but S(1), S(2), ... ===========================
+    // Program order per tile: G, then (as the exp groups deliver them) the products that read W and P; the next
+    // tile's G follows at once.  The tensor pipe runs one thread's products in order, so the G columns are never
+    // overwritten before the products that read W and P there have done so.
     {
       constexpr int fmt = kBf16 ? 1 : 0;
       constexpr uint32_t idesc_kk = umma_idesc(fmt, 0, 0, 128, 128);    // both operands K-major
@@ -314,9 +308,6 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
 #endif
           }
           umma_commit_w(&s.s_full);
-#ifdef LUCID_TRACE
-          umma_commit_w(&s.tr_done[1]);
-#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 12, gt);
           return true;
         };
@@ -341,16 +332,9 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
 #endif
           }
           umma_commit_w(&s.g_full);
-#ifdef LUCID_TRACE
-          umma_commit_w(&s.tr_done[0]);
-#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 10, g);
           if (q == n - 2) umma_commit_w(&s.g_done);      // V'_i is no longer needed: X_i may take its buffer
-          // ---- S(q+1): region B is free once every exp thread has S(q) in registers ----
-          if (!wait_barrier(&s.s_loaded, gf & 1, cta_abort, ctl, limit, chain, i, RD_S_LOADED)) { alive = false; break; }
-          if (leader) LUCID_TR(args.trace, 2, trc, 11, g);
-          if (!issue_s(g + 1)) { alive = false; break; }
-          if (q + 1 == n - 1) umma_commit_w(&s.kt_empty[(g + 1) & 1]);   // S_l was K_l's only reader
+          // (S(q+1) is issued by the other issuing warp as soon as every exp thread has S(q) in registers)
           // ---- ACC_dK += W K_j, then ACC_dV += P dV_j ----
           const uint64_t dbv_mn = d_vr0_mn + st * (kTileBytes >> 4);
           const uint64_t dbk_mn = d_kr0_mn + st * (kTileBytes >> 4);
@@ -363,15 +347,15 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
             }
           }
           if (!wait_barrier(&s.pw_full[0], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
+          // K_j: its S product (from the other warp for q > 0) is long complete, so this wait is over at once; it
+          // is made because this warp's products read the tile too
+          if (!wait_barrier(&s.kt_full[st], (g >> 1) & 1, cta_abort, ctl, limit, chain, i, RD_KT_FULL)) { alive = false; break; }
           tc_fence_after_sync();
           if (leader) LUCID_TR(args.trace, 2, trc, 13, g);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             umma_ts_w(tmem + kRdAccK, tmem + kRdW + 8 * ks, dbk_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.kt_empty[st]);
-#ifdef LUCID_TRACE
-          umma_commit_w(&s.tr_done[2]);
-#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 14, g);
           if (!wait_barrier(&s.pw_full[1], gf & 1, cta_abort, ctl, limit, chain, i, RD_PW_FULL)) { alive = false; break; }
           tc_fence_after_sync();
@@ -380,9 +364,6 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
           for (int ks = 0; ks < 8; ++ks)
             umma_ts_w(tmem + kRdAcc, tmem + kRdP + 8 * ks, dbv_mn + ks * (2048 >> 4), idesc_tb, (q | ks) ? 1u : 0u);
           umma_commit_w(&s.vt_empty[st]);
-#ifdef LUCID_TRACE
-          umma_commit_w(&s.tr_done[3]);
-#endif
           if (leader) LUCID_TR(args.trace, 2, trc, 16, g);
           ++gf;
         }
@@ -433,28 +414,58 @@ revdk_kernel(const __grid_constant__ CUtensorMap tm_k,     // K,   box 64 x 128
         }
         umma_commit_w(&s.out_full);
       }
-#ifdef LUCID_TRACE
-      s.tr_stop = 1;
-#endif
     }
   } else if (warp == 3) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRdRegsService));   // fills the service warpgroup
-#ifdef LUCID_TRACE
-    if (lane == 0 && args.trace != nullptr) {
-      // debugging builds: the clock at which each group of products completed on the tensor pipe (tags 70-73:
-      // G, S, W K_j, P dV_j; q = how many of that kind completed before)
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRdRegsService));
+    // =========================== the issuer of S(1), S(2), ... of every item ===========================
+    // S(q+1) needs K_j in shared memory and region B, which is free as soon as every exp thread holds S(q) in
+    // registers; nothing else.  Issued from the other warp it stood, with its waits, in the middle of the chain
+    // G(q) -> W(q), P(q) -> their products -> G(q+1) that bounds a tile, and the tensor pipe runs two warps'
+    // products closer together than one warp's.  The FIRST S of an item stays with the other warp, behind the
+    // closing product of the item before in that warp's program order: that product reads -Q from region B, and
+    // this way no barrier has to say across warps that it is done.  This warp touches region B only between
+    // s_loaded of a tile and s_full of the next, when the other warp has no product on it; it waits for every
+    // s_loaded phase and for the ticket of every item, so no barrier it reads can run two phases ahead of it.
+    {
+      constexpr int fmt = kBf16 ? 1 : 0;
+      constexpr uint32_t idesc_kk = umma_idesc(fmt, 0, 0, 128, 128);
+      const uint64_t d_ki = umma_smem_desc(smem_u32(s.ki), 16, 1024);
+      const uint64_t d_kr0 = umma_smem_desc(smem_u32(s.kring[0]), 16, 1024);     // stage: + 32 KiB
+      uint32_t g0 = 0, gf = 0;       // tiles and full tiles of the items before (as counted by the other roles)
+      bool alive = true;
       int trc = 0;
-      uint32_t cnt[4] = {0, 0, 0, 0};
-      volatile int* stop = &s.tr_stop;
-      while (!*stop && !*cta_abort) {
-        for (int b = 0; b < 4; ++b)
-          if (mbar_try_wait(&s.tr_done[b], cnt[b] & 1)) {
-            LUCID_TR(args.trace, 7, trc, 70 + b, cnt[b]);
-            ++cnt[b];
+      (void)trc;
+      const bool leader = lane == 0;
+      (void)leader;
+      for (int it = 0; alive; ++it) {
+        const int slot = it & 1;
+        if (!wait_barrier(&s.tk_full[slot], (it >> 1) & 1, cta_abort, ctl, limit, -1, -1, RD_TK_FULL)) break;
+        const int ticket = s.tk_slot[slot];
+        __syncwarp();
+        mbar_arrive_w(&s.tk_empty[slot]);
+        int chain, i, n;
+        if (!item_geometry(ticket, chain, i, n)) break;
+        for (int q = 1; q < n; ++q, ++gf) {
+          // every exp thread holds S(q-1), a full tile (q - 1 <= n - 2); K_i is in place (S(0) has used it)
+          if (!wait_barrier(&s.s_loaded, gf & 1, cta_abort, ctl, limit, chain, i, RD_S_LOADED)) { alive = false; break; }
+          const uint32_t gt = g0 + q;
+          const uint32_t st = gt & 1;
+          if (!wait_barrier(&s.kt_full[st], (gt >> 1) & 1, cta_abort, ctl, limit, chain, i, RD_KT_FULL)) { alive = false; break; }
+          tc_fence_after_sync();
+          if (leader) LUCID_TR(args.trace, 5, trc, 18, gt);
+          const uint64_t dbk = d_kr0 + st * (kTileBytes >> 4);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+            umma_ss_w(tmem + kRdS, d_ki + off, dbk + off, idesc_kk, k ? 1u : 0u);
           }
+          umma_commit_w(&s.s_full);
+          if (q == n - 1) umma_commit_w(&s.kt_empty[st]);     // the newest predecessor: S_l is K_l's only reader
+          if (leader) LUCID_TR(args.trace, 5, trc, 12, gt);
+        }
+        g0 += n;
       }
     }
-#endif
   } else if (warp >= 4) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRdRegsExp));
     // =========================== exp groups + epilogue ===========================
