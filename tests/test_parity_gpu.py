@@ -460,11 +460,13 @@ def test_upper_dk_accumulated_by_the_reverse_solve(ops, dtype):
     """With more than two systems the reverse solve also accumulates the upper-triangle dK terms of the tiles it
     streams and the dK kernel runs the rest.  Against the plain pair of kernels (reverse solve, dK over all
     tiles): dV bit-identical (same products in the same order), dK equal to rounding (the same terms summed in
-    two fp32 pieces), both within the gates of the oracle; T = 1, 2, 3 exercise the row-blocks without full tiles."""
+    two fp32 pieces), both within the gates of the oracle; T = 1, 2, 3 exercise the row-blocks without full tiles,
+    and the last two shapes (32 systems of T = 4 and of T = 2) make every CTA take several such row-blocks in a row,
+    the case in which the two issuing warps of the kernel are furthest apart."""
     from lucid_kernels_b200 import _cabi
 
     lib = _cabi.load()
-    for B, N, H in ((1, 128, 3), (1, 256, 3), (1, 384, 3), (1, 1024, 3), (2, 2048, 8)):
+    for B, N, H in ((1, 128, 3), (1, 256, 3), (1, 384, 3), (1, 1024, 3), (2, 2048, 8), (4, 512, 8), (2, 256, 16)):
         K, V, G = orc.make_inputs(B, N, H, dtype=dtype, seed=17)
         Kc, Vc, Gc = K.cuda(), V.cuda(), G.cuda()
         vp = ops._forward_sub_fwd(Kc, Vc, check=True)
