@@ -74,7 +74,8 @@ size_t lucid_fwd_workspace_bytes(int B, int N, int H);
  * window_size=None); otherwise only the last `window_blocks` blocks are subtracted, 0 meaning none at all,
  * i.e. only the diagonal-block solve (n_block_count = min(m_block, window_size), forward_sub_fwd.py:518-519).
  * `chain_group` = how many (batch, head) systems the scheduler advances together (0 = choose from the
- * problem size so that their K and V' fit the L2 cache). */
+ * problem size: as many as keep the K and V' they stream again and again at about the size of the L2 cache,
+ * in groups of equal size). */
 int lucid_fwd_sub(const void* k, const void* v, void* v_prime, const int64_t k_strides[3],
                   const int64_t v_strides[3], const int64_t vp_strides[3], int B, int N, int H, int D, int dtype,
                   int flags, int window_blocks, int chain_group, void* workspace, size_t workspace_bytes,

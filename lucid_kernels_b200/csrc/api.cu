@@ -107,23 +107,33 @@ static int bshd_map(CUtensorMap* m, bool bf16, const void* p, const int64_t st[3
   return make_tmap_16bit(m, bf16, p, 4, dims, strides, box_rows) ? LUCID_E_TENSOR_MAP : 0;
 }
 
-static int auto_group(int C, int N, int requested) {
+static int auto_group(int C, int N, int requested, bool backward) {
   if (requested > 0) return requested < C ? requested : C;
-  // K and Y of one chain take N * 512 bytes.  Long chains (T >= 256) are throughput-bound and run best with a
-  // group's working set at about half of the 126 MB L2 (measured on B200, forward, ms for groups of
-  // 2/4/8/16 at B*H=16, N=32768: 6.2/4.6/5.0/5.6; 1/2 at B*H=8, N=131072: 38.7/40.4; 2/4/8 at B*H=8, N=65536:
-  // 9.4/10.0/10.9); short chains are bound by the chain latency, which every group pays once, so they take
-  // the whole L2 (4/8/16 at B*H=16, N=16384: 2.4/1.8/1.5).  The groups are made equal in size.
+  // K and Y of one chain take N * 512 bytes, and every row-block of a group streams them again and again: TMA
+  // delivers such tiles at 65 bytes per clock per SM while the streamed set is below about 64 MB, at 47-53 beyond
+  // that; but a group must also hold enough chains to keep all SMs busy, and every group pays the chain latency of
+  // its first row-blocks.  Measured on B200, forward + backward of the present kernels in ms, by group size:
+  //   B*H=16, N=32768:   4: 4.4 + 13.2   6: 4.8 + 12.6   8: 4.7 + 13.3   16: 5.1 + 14.2   (benchmark step, one graph:
+  //                      17.5 / 16.9 / 17.0 ms with 4 / 6 / 8 for both)
+  //   B*H=8,  N=65536:   2: 9.8 + 25.8   3: 10.4 + 25.9   4: 9.0 + 24.8   8: 10.1 + 26.0
+  //   B*H=8,  N=131072:  1: 39.4 + 107.4   2: 39.2 + 98.2   3: 41.9 + 97.3   4: 43.5 + 96.5
+  //   B*H=4,  N=65536:   1: 7.0 + 16.2   2: 5.4 + 13.0   4: 4.4 + 12.5
+  //   B*H=16, N=16384:   4: 1.8 + 4.2   8: 1.3 + 3.3   16: 1.3 + 3.4
+  // The forward does best with K and Y of a group at about the size of the L2 (128 MiB); the backward, which streams
+  // three tensors per tile in its dK part, with 104 MiB but never fewer than four chains.  The groups are made
+  // equal in size.
   const long long per_chain = (long long)N * 512;
-  const long long budget = (N / kBlock >= 256) ? (72ll << 20) : (144ll << 20);
+  const long long budget = backward ? (104ll << 20) : (128ll << 20);
   long long gmax = budget / per_chain;
-  if (gmax < 1) gmax = 1;
+  const long long floor_chains = backward ? 4 : 1;
+  if (gmax < floor_chains) gmax = floor_chains;
   if (gmax >= C) return C;
   const long long ng = (C + gmax - 1) / gmax;
   return (int)((C + ng - 1) / ng);
 }
 
-static Problem make_problem(int B, int N, int H, int flags, int window, int group, float k_scale) {
+static Problem make_problem(int B, int N, int H, int flags, int window, int group, float k_scale,
+                            bool backward = false) {
   Problem p;
   p.exp_scale = kLog2e * k_scale * k_scale;
   p.out_scale = k_scale * k_scale;
@@ -132,7 +142,7 @@ static Problem make_problem(int B, int N, int H, int flags, int window, int grou
   p.H = H;
   p.T = N / kBlock;
   p.C = B * H;
-  p.group = auto_group(p.C, N, group);
+  p.group = auto_group(p.C, N, group, backward);
   // Optionally the short, latency-bound first row-blocks of every chain are scheduled for all chains
   // together before the groups start.  Off by default: on B=2, N=32768, H=8 a sweep over 0 / 48 / 96 / 144 /
   // 192 / 256 steps gave 4.7-5.9 / 5.0-5.2 / 5.1-5.2 / 5.2-5.4 / 5.5 / 6.1 ms for the forward, i.e. no gain
@@ -441,7 +451,7 @@ int lucid_bwd_sub_scaled(const void* k, const void* v_prime, const void* dv_prim
   cudaError_t e = cudaMemsetAsync(ws, 0, lay.x, stream);
   if (e != cudaSuccess) return (int)e;
   const bool bf16 = dtype == LUCID_DTYPE_BF16;
-  const Problem p = make_problem(B, N, H, flags, -1, chain_group, k_scale);
+  const Problem p = make_problem(B, N, H, flags, -1, chain_group, k_scale, mode == LUCID_BWD_COMBINED);
   const int sms = sm_count();
   if (sms <= 0) return LUCID_E_NO_DEVICE;
   const int CT = p.C * p.T;

@@ -216,6 +216,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_x);
+      const uint64_t pol_once = l2_policy_evict_first();     // X_i: read once per row-block
       uint32_t u = 0;
       bool alive = true;
       int trc = 0;
@@ -279,16 +280,16 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
           }
           if (alive && !x_loaded && mbar_try_wait(&s.xr_free, (it & 1) ^ 1)) {
             mbar_expect_tx(&s.x_full, kTileBytes);
-            tma_load_2d(s.x, &tm_x, &s.x_full, 0, (chain * T + i) * kBlock);
-            tma_load_2d(s.x + kHalfBytes, &tm_x, &s.x_full, 64, (chain * T + i) * kBlock);
+            tma_load_2d_hint(s.x, &tm_x, &s.x_full, 0, (chain * T + i) * kBlock, pol_once);
+            tma_load_2d_hint(s.x + kHalfBytes, &tm_x, &s.x_full, 64, (chain * T + i) * kBlock, pol_once);
             x_loaded = true;
           }
         }
         if (alive && !x_loaded) {
           if (!wait_barrier(&s.xr_free, (it & 1) ^ 1, cta_abort, ctl, limit, chain, i, BAR_XR_FREE)) break;
           mbar_expect_tx(&s.x_full, kTileBytes);
-          tma_load_2d(s.x, &tm_x, &s.x_full, 0, (chain * T + i) * kBlock);
-          tma_load_2d(s.x + kHalfBytes, &tm_x, &s.x_full, 64, (chain * T + i) * kBlock);
+          tma_load_2d_hint(s.x, &tm_x, &s.x_full, 0, (chain * T + i) * kBlock, pol_once);
+          tma_load_2d_hint(s.x + kHalfBytes, &tm_x, &s.x_full, 64, (chain * T + i) * kBlock, pol_once);
         }
       }
     }
@@ -298,6 +299,7 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
     if (lane == 0) {
       tma_prefetch_desc(&tm_in);
       tma_prefetch_desc(&tm_out);
+      const uint64_t pol_once = l2_policy_evict_first();     // the row-block's own right-hand side: read once
       uint32_t u = 0;
       bool alive = true;
       int trc = 0;
@@ -315,8 +317,8 @@ __device__ __forceinline__ void solve_body(const CUtensorMap& tm_k,     // K, bo
         bool vi_loaded = false;
         auto load_vi = [&]() {
           mbar_expect_tx(&s.vi_full, kTileBytes);
-          tma_load_4d(s.rhs, &tm_in, &s.vi_full, 0, i * kBlock, h, b);
-          tma_load_4d(s.rhs + kHalfBytes, &tm_in, &s.vi_full, 64, i * kBlock, h, b);
+          tma_load_4d_hint(s.rhs, &tm_in, &s.vi_full, 0, i * kBlock, h, b, pol_once);
+          tma_load_4d_hint(s.rhs + kHalfBytes, &tm_in, &s.vi_full, 64, i * kBlock, h, b, pol_once);
           vi_loaded = true;
         };
         unsigned long long waited = 0;
