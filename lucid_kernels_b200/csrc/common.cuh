@@ -133,7 +133,10 @@ __device__ __forceinline__ bool wait_flag(const int* flag, volatile int* cta_abo
 // `probe_row` of the chain whose flags start at `chain_flags`) and returns the number of leading tiles that need
 // no flag check of their own: n - kFlagProbe + 1 if that flag is up, else 0.  The proxy fence that must stand
 // between an acquire in the generic proxy and TMA loads of the data is issued here when the answer is not 0.
-constexpr int kFlagProbe = 48;
+#ifndef LUCID_FLAG_PROBE
+#define LUCID_FLAG_PROBE 48
+#endif
+constexpr int kFlagProbe = LUCID_FLAG_PROBE;
 __device__ __forceinline__ int flags_known_up(const int* chain_flags, int n, int probe_row) {
   if (n <= kFlagProbe) return 0;
   if (ld_acquire_gpu(chain_flags + probe_row) < kFlagComplete) return 0;
