@@ -620,6 +620,10 @@ def main():
         # where an end-to-end step goes: the same loop with only the copies, and with only the kernels
         e2e["breakdown_ms"] = dict(copies_only=timed_e2e(n_e2e, kernels=False), kernels_only=timed_e2e(n_e2e, copies=False),
                                    both=ms_e2e)
+        # The timed region starts with an empty pipeline and ends when the last download has landed, so it holds
+        # one upload and one download that nothing overlaps; the same loop over four times as many steps shows
+        # how much of the per-step figure that is.
+        e2e["ms_per_step_over_4x_steps"] = timed_e2e(4 * n_e2e)
         if not args.no_parity:
             torch.cuda.synchronize()
             e2e["host_outputs_equal_device_outputs"] = bool(
