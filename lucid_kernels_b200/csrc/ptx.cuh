@@ -170,7 +170,7 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
 // The same loads with an L2 eviction policy.  Tiles that are read once per row-block (its own right-hand side, its
 // inverse block) are loaded evict-first, so that they do not push out the K_j and Y_j tiles every row-block of the
 // scheduler group streams again and again: the rate at which TMA delivers those drops from 65 to 47 bytes per clock
-// per SM once the re-read set outgrows what one die's half of the L2 holds.
+// per SM once the re-read set grows past about 64 MB (measured, csrc/probe.cu).
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
