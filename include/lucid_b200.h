@@ -211,6 +211,11 @@ void lucid_set_upper_in_solve(int on);
  * settings on the current device, else 0 (benchmarks use it to label what they measured). */
 int lucid_query_upper_in_solve(int B, int N, int H);
 
+/* How many (batch, head) systems the scheduler advances together when `chain_group` is 0: for the forward
+ * solve (and the dV-only backward), or with combined_backward != 0 for the combined backward.  Plain host
+ * arithmetic (no device needed); 0 for an invalid shape. */
+int lucid_query_chain_group(int B, int N, int H, int combined_backward);
+
 /* Kernel variant of the stand-alone solves: bit 0 = the S products read K_i from tensor memory instead of
  * shared memory (two S buffers instead of three).  No counterpart in the reference. */
 void lucid_set_solve_variant(int bits);

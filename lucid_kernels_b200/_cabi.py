@@ -31,7 +31,7 @@ EXPORTS = ("lucid_workspace_bytes", "lucid_fwd_sub", "lucid_bwd_sub", "lucid_rea
            "lucid_profile_next_call", "lucid_set_head_steps", "lucid_set_group_overlap", "lucid_set_dk_split", "lucid_fwd_sub_static",
            "lucid_set_fused_backward", "lucid_fwd_sub_scaled", "lucid_bwd_sub_scaled",
            "lucid_set_pair_solve", "lucid_set_pair_limits", "lucid_fwd_workspace_bytes", "lucid_stream_capture_id", "lucid_query_pair_solve", "lucid_set_solve_variant", "lucid_set_upper_in_solve", "lucid_query_upper_in_solve",
-           "lucid_probe_tma_delivery")
+           "lucid_probe_tma_delivery", "lucid_query_chain_group")
 
 
 class LucidKernelError(RuntimeError):
@@ -101,6 +101,8 @@ def load() -> ctypes.CDLL:
                                              c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
                                              c.c_int, c.c_float, c.c_void_p, c.c_size_t, c.c_void_p]
         lib.lucid_read_status.restype = c.c_int
+        lib.lucid_query_chain_group.restype = c.c_int
+        lib.lucid_query_chain_group.argtypes = [c.c_int, c.c_int, c.c_int, c.c_int]
         lib.lucid_probe_tma_delivery.restype = c.c_int
         lib.lucid_probe_tma_delivery.argtypes = [c.c_void_p, _I64x3, c.c_int, c.c_int, c.c_int, c.c_int, c.c_int,
                                                  c.c_int, c.c_void_p, c.c_int, c.c_void_p]
@@ -257,7 +259,7 @@ def tma_delivery_rate(t: torch.Tensor, slots: int = 4, boxes_per_sm: int = 4000)
             ev0.record(stream)
         rc = lib.lucid_probe_tma_delivery(t.data_ptr(), strides3(t), B, N, H, dtype_code(t.dtype), slots,
                                           boxes_per_sm, clocks.data_ptr(), sms, stream.cuda_stream)
-        check_rc(rc, "lucid_probe_tma_delivery")
+        check_rc(rc, "lucid_probe_tma_delivery", "lucid_query_chain_group")
         if timed:
             ev1.record(stream)
     stream.synchronize()

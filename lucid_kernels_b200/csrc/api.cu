@@ -322,6 +322,11 @@ int lucid_query_upper_in_solve(int B, int N, int H) {
   return (!fuse && g_upper_in_solve) ? 1 : 0;
 }
 
+int lucid_query_chain_group(int B, int N, int H, int combined_backward) {
+  if (B <= 0 || N <= 0 || H <= 0 || N % kBlock) return 0;
+  return auto_group(B * H, N, 0, combined_backward != 0);
+}
+
 void lucid_set_pair_solve(int max_chains) { g_pair_max_chains = max_chains; }
 
 void lucid_set_pair_limits(int max_chains, int max_row_blocks) {

@@ -48,6 +48,25 @@ def test_workspace_size_and_status_strings(lib):
     assert b"published" in lib.lucid_status_string(2)
 
 
+def test_scheduler_group_sizes(lib):
+    """The automatic group size (chain_group = 0): K and V' of a group at about the size of the L2 in the forward,
+    104 MiB but at least four systems in the combined backward, groups of equal size, never more than there are
+    systems.  The shapes are those the rule was measured on."""
+    q = lib.lucid_query_chain_group
+    assert q(1, 100, 1, 0) == 0                                   # invalid shape
+    assert (q(2, 32768, 8, 0), q(2, 32768, 8, 1)) == (8, 6)       # the benchmark: 16 systems of N = 32768
+    assert (q(1, 65536, 8, 0), q(1, 65536, 8, 1)) == (4, 4)
+    assert (q(1, 131072, 8, 0), q(1, 131072, 8, 1)) == (2, 4)
+    assert (q(1, 65536, 4, 0), q(1, 65536, 4, 1)) == (4, 4)
+    assert (q(2, 16384, 8, 0), q(2, 16384, 8, 1)) == (16, 8)
+    assert (q(1, 32768, 2, 0), q(1, 32768, 2, 1)) == (2, 2)       # the 8-GPU share: all of its systems
+    assert (q(1, 8192, 8, 0), q(1, 8192, 8, 1)) == (8, 8)
+    for B, N, H in ((3, 32768, 5), (1, 1 << 20, 3), (7, 128, 1)):
+        for bwd in (0, 1):
+            g = q(B, N, H, bwd)
+            assert 1 <= g <= B * H
+
+
 def test_argument_validation_without_gpu(lib):
     I3 = ctypes.c_int64 * 3
     st = I3(128 * 4 * 512, 128 * 4, 128)
