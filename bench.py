@@ -759,9 +759,12 @@ def main():
                                 sharding=f"{nsys} (batch, head) systems over {world} rank(s), no collective",
                                 l2="inputs (3 x 128 MiB per step at N=32768) exceed the 126 MB L2; no flush",
                                 launch=launch_mode,
-                                scheduler_groups=f"{lib.lucid_query_chain_group(1, N, n_local, 0)} systems per group in "
-                                                 f"the forward solve, {lib.lucid_query_chain_group(1, N, n_local, 1)} in "
-                                                 "the backward (on rank 0)",
+                                scheduler_groups=(f"{os.environ['LUCID_B200_CHAIN_GROUP']} systems per group (set by "
+                                                  "LUCID_B200_CHAIN_GROUP)"
+                                                  if os.environ.get("LUCID_B200_CHAIN_GROUP", "0") not in ("", "0") else
+                                                  f"{lib.lucid_query_chain_group(1, N, n_local, 0)} systems per group in "
+                                                  f"the forward solve, {lib.lucid_query_chain_group(1, N, n_local, 1)} in "
+                                                  "the backward (on rank 0)"),
                                 seed=0),
                     frac_of_bf16_peak=value / (world * peaks["bf16_tflops"]),
                     eager=dict(ms_per_step=ms_eager, value=total_flops / (ms_eager * 1e-3) / 1e12, steps=n_prof,
